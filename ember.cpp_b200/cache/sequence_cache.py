@@ -13,7 +13,8 @@ its one sequence (graph_ir.h:310, 462), a window per layer where a model has one
   with storage of its own: per application of the schedule one K and one V tensor of shape
   [pages, kv_heads, 64, head_dim], and one pool of page numbers shared by the group's layers.  A
   sequence holds ceil(length / 64) pages of a full group; a window group gives back the pages that
-  lie wholly before the window.
+  lie wholly before the window, except those that hold one of the first `keep_first` positions
+  where the group's mixers keep these visible for good.
 * `max_tokens` sizes every group's pool: the most positions that live sequences hold at any time,
   each sequence's count rounded up to a multiple of 64.
 * State tensors are [slots, *shape] float32 per application that asks for one, set to the part's
@@ -42,9 +43,10 @@ class CacheGroup:
     def __init__(self, need: CacheNeed, apps: list[int], n_pages: int, n_slots: int, dtype, device):
         self.need, self.apps = need, list(apps)
         self.pages = Pool(n_pages, "page")
-        shape = (n_pages, need.kv_heads, PAGE, need.head_dim)
-        self.k = [torch.zeros(shape, dtype=dtype, device=device) for _ in apps]
-        self.v = [torch.zeros(shape, dtype=dtype, device=device) for _ in apps]
+        self.k = [torch.zeros((n_pages, need.kv_heads, PAGE, need.head_dim), dtype=dtype, device=device) for _ in apps]
+        self.v = [torch.zeros((n_pages, need.kv_heads, PAGE, need.v_dim), dtype=dtype, device=device) for _ in apps]
+        # blocks that hold one of the first positions a window group keeps for good
+        self.kept_blocks = -(-need.keep_first // PAGE) if need.kind == "window" else 0
         # per slot: page number of each 64-position block, -1 where none is held
         self.held: list[list[int]] = [[] for _ in range(n_slots)]
 
@@ -76,9 +78,10 @@ class CacheGroup:
         return fresh
 
     def trim(self, slot: int, length: int) -> None:
-        """Gives back what no later query can read (window groups), or what lies past `length`."""
+        """Gives back what no later query can read (window groups; never the blocks of the kept first
+        positions), or what lies past `length`."""
         have = self.held[slot]
-        for b in range(min(self.first_needed_block(length), len(have))):
+        for b in range(self.kept_blocks, min(self.first_needed_block(length), len(have))):
             if have[b] >= 0:
                 self.pages.give_back(have[b])
                 have[b] = -1
@@ -113,8 +116,9 @@ class CacheView:
         # a kernel may warm it while it reads this one
         n = len(group.k)
         self.following = (group.k[(local + 1) % n], group.v[(local + 1) % n]) if n > 1 else None
-        self.kv_heads, self.head_dim = group.need.kv_heads, group.need.head_dim
+        self.kv_heads, self.head_dim, self.value_dim = group.need.kv_heads, group.need.head_dim, group.need.v_dim
         self.window = group.need.window if group.need.kind == "window" else 0
+        self.keep_first = group.need.keep_first if group.need.kind == "window" else 0
 
 
 class SequenceCache:
@@ -186,6 +190,30 @@ class SequenceCache:
         if not self.slots.is_held(slot):
             raise CacheError(f"slot {slot} is not open")
         return self.lengths[slot]
+
+    # ------------------------------------------------------------------ state kept aside
+    def _state_tensors(self):
+        for state in self.states:
+            if isinstance(state, dict):
+                yield from state.values()
+            elif state is not None:
+                yield state
+
+    def save_states(self, slots) -> list:
+        """Copies of the state rows of `slots` in every state tensor (for `restore_states`).  A step that
+        is run twice (once launch by launch before it is captured as a graph, then replayed) must
+        find the same state both times: keys and values are written alike twice, a recurrence's state
+        is not."""
+        rows = [s for s in slots if s >= 0]
+        if not rows:
+            return []
+        index = torch.tensor(rows, dtype=torch.long, device=self.device)
+        return [(t, index, t.index_select(0, index)) for t in self._state_tensors()]
+
+    @staticmethod
+    def restore_states(saved: list) -> None:
+        for t, index, rows in saved:
+            t.index_copy_(0, index, rows)
 
     # ------------------------------------------------------------------ a step's storage
     def reserve(self, step: list[tuple[int, int]]) -> list[list[tuple[int, int]]]:

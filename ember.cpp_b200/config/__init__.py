@@ -2,6 +2,7 @@
 from .base import (Architecture, ConfigError, ModelConfig, architectures, config_from_dict, get_architecture,
                    load_config, register_architecture)
 from .gpt2 import GELU_FORMS, GPT2Config
+from .nipolorn import NipolornConfig
 
-__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "architectures",
+__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "NipolornConfig", "architectures",
            "config_from_dict", "get_architecture", "load_config", "register_architecture"]

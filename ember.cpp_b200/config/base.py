@@ -116,8 +116,10 @@ def get_architecture(name: str) -> Architecture:
 
 def config_from_dict(d: dict[str, Any]) -> ModelConfig:
     arch = d.get("architectures")
+    if arch is None and isinstance(d.get("architecture"), str):      # some models name it with one string
+        arch = [d["architecture"]]
     if not isinstance(arch, list) or not arch or not isinstance(arch[0], str):
-        raise ConfigError("config.json has no 'architectures' list naming the model class")
+        raise ConfigError("config.json has no 'architectures' list (or 'architecture' string) naming the model class")
     return get_architecture(arch[0]).config_cls.from_dict(d)
 
 

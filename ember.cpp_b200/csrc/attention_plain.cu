@@ -20,7 +20,7 @@ template <typename T, bool VEC>
 __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T* __restrict__ vc,
                                 const int* __restrict__ positions, const int* __restrict__ token_seq,
                                 const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks,
-                                int q_width, int kv_heads, int hd) {
+                                int q_width, int kv_heads, int hd, int vd) {
   constexpr int kVec = VEC ? 16 / (int)sizeof(T) : 1;
   pdl_trigger();
   pdl_wait();
@@ -30,36 +30,56 @@ __global__ void kv_store_kernel(const T* __restrict__ qkv, T* __restrict__ kc, T
   const int p = positions[t];
   const int page = pages[s * max_blocks + p / kPage];
   if (page < 0) return;
-  const int kv_width = kv_heads * hd;
-  const T* src = qkv + (size_t)t * (q_width + 2 * kv_width) + q_width;
-  for (int i = threadIdx.x * kVec; i < kv_width; i += blockDim.x * kVec) {
-    const int h = i / hd, d = i % hd;
-    const size_t dst = (((size_t)page * kv_heads + h) * kPage + (p % kPage)) * hd + d;
-    if constexpr (VEC) {
-      const uint4 k = __ldcg(reinterpret_cast<const uint4*>(src + i));
-      const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + kv_width + i));
-      *reinterpret_cast<uint4*>(kc + dst) = k;
-      *reinterpret_cast<uint4*>(vc + dst) = v;
-    } else {
-      const T k = __ldcg(src + i), v = __ldcg(src + kv_width + i);
-      kc[dst] = k;
-      vc[dst] = v;
+  const int k_width = kv_heads * hd, v_width = kv_heads * vd;
+  const T* src = qkv + (size_t)t * (q_width + k_width + v_width) + q_width;
+  if (vd == hd) {
+    for (int i = threadIdx.x * kVec; i < k_width; i += blockDim.x * kVec) {
+      const int h = i / hd, d = i % hd;
+      const size_t dst = (((size_t)page * kv_heads + h) * kPage + (p % kPage)) * hd + d;
+      if constexpr (VEC) {
+        const uint4 k = __ldcg(reinterpret_cast<const uint4*>(src + i));
+        const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + k_width + i));
+        *reinterpret_cast<uint4*>(kc + dst) = k;
+        *reinterpret_cast<uint4*>(vc + dst) = v;
+      } else {
+        const T k = __ldcg(src + i), v = __ldcg(src + k_width + i);
+        kc[dst] = k;
+        vc[dst] = v;
+      }
     }
+    return;
   }
+  // values with a row size of their own: keys and values one after the other, value by value
+  for (int i = threadIdx.x; i < k_width; i += blockDim.x)
+    kc[(((size_t)page * kv_heads + i / hd) * kPage + (p % kPage)) * hd + i % hd] = __ldcg(src + i);
+  for (int i = threadIdx.x; i < v_width; i += blockDim.x)
+    vc[(((size_t)page * kv_heads + i / vd) * kPage + (p % kPage)) * vd + i % vd] = __ldcg(src + k_width + i);
 }
+
+EMBER_API int ember_kv_store_v(const void* qkv, void* kc, void* vc, const int* positions, const int* token_seq,
+                               const int* seq_slot, const int* pages, int max_blocks, int T, int n_heads, int kv_heads,
+                               int hd, int vd, int dtype, cudaStream_t stream);
 
 EMBER_API int ember_kv_store(const void* qkv, void* kc, void* vc, const int* positions, const int* token_seq,
                              const int* seq_slot, const int* pages, int max_blocks, int T, int n_heads, int kv_heads,
                              int hd, int dtype, cudaStream_t stream) {
-  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && hd > 0 && max_blocks > 0, "kv_store: bad sizes");
+  return ember_kv_store_v(qkv, kc, vc, positions, token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, hd,
+                          dtype, stream);
+}
+
+// The same with values of `vd` per head (rows of the step: q | k | v with n_heads*hd, kv_heads*hd, kv_heads*vd values).
+EMBER_API int ember_kv_store_v(const void* qkv, void* kc, void* vc, const int* positions, const int* token_seq,
+                               const int* seq_slot, const int* pages, int max_blocks, int T, int n_heads, int kv_heads,
+                               int hd, int vd, int dtype, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && hd > 0 && vd > 0 && max_blocks > 0, "kv_store: bad sizes");
   EMBER_CHECK(dtype == EMBER_F32 || dtype == EMBER_BF16, "kv_store: element type %d", dtype);
   const int qw = n_heads * hd;
   // 16-byte copies where every head's row, and so every row of the activations, is a multiple of 16 bytes
-  const bool vec = hd * (dtype == EMBER_F32 ? 4 : 2) % 16 == 0;
+  const bool vec = vd == hd && hd * (dtype == EMBER_F32 ? 4 : 2) % 16 == 0;
   cudaError_t e;
 #define EMBER_KV_STORE(T, VEC)                                                                                           \
   e = launch_pdl(kv_store_kernel<T, VEC>, dim3(T_tokens), dim3(128), 0, stream, (const T*)qkv, (T*)kc, (T*)vc, positions, \
-                 token_seq, seq_slot, pages, max_blocks, qw, kv_heads, hd)
+                 token_seq, seq_slot, pages, max_blocks, qw, kv_heads, hd, vd)
   const int T_tokens = T;
   if (dtype == EMBER_F32) {
     if (vec) EMBER_KV_STORE(float, true); else EMBER_KV_STORE(float, false);
@@ -119,17 +139,17 @@ __global__ void __launch_bounds__(128)
 attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, const T* __restrict__ vc,
                        T* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                        const int* __restrict__ seq_slot, const int* __restrict__ pages, int max_blocks, int T_tokens,
-                       int n_heads, int kv_heads, int hd, float scale, int window) {
+                       int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first) {
   __shared__ float q_s[4][kMaxHeadDim];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int item = blockIdx.x * 4 + warp;
   if (item >= T_tokens * n_heads) return;  // whole warps leave together
   const int t = item / n_heads, h = item % n_heads;
-  const int qkv_width = (n_heads + 2 * kv_heads) * hd;
-  T* o = out + (size_t)t * n_heads * hd + (size_t)h * hd;
+  const int qkv_width = (n_heads + kv_heads) * hd + kv_heads * vd;
+  T* o = out + (size_t)t * n_heads * vd + (size_t)h * vd;
   const int s = token_seq[t];
   if (seq_slot[s] < 0) {
-    for (int d = lane; d < hd; d += 32) o[d] = from_float<T>(0.f);
+    for (int d = lane; d < vd; d += 32) o[d] = from_float<T>(0.f);
     return;
   }
   const int p = positions[t];
@@ -145,15 +165,19 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
 
-  for (int base = lo; base <= p; base += 32) {
-    const int j = base + lane;
-    const int page = j <= p ? my_pages[j / kPage] : -1;
+  // The visible keys in order: the kept first positions that lie before the window, then the window.
+  const int n_kept = window > 0 ? min(keep_first, lo) : 0;
+  const int n_keys = n_kept + p - lo + 1;
+  for (int base = 0; base < n_keys; base += 32) {
+    const int idx = base + lane;
+    const int j = idx < n_kept ? idx : lo + idx - n_kept;
+    const int page = idx < n_keys ? my_pages[j / kPage] : -1;
     const bool valid = page >= 0;  // a page that is not held contributes nothing and is never read
-    size_t row = 0;  // element offset of key/value row j of head g
+    size_t row = 0;  // row number of key/value j of head g in the cache
     float sc = -INFINITY;
     if (valid) {
-      row = (((size_t)page * kv_heads + g) * kPage + (j % kPage)) * hd;
-      const T* k = kc + row;
+      row = ((size_t)page * kv_heads + g) * kPage + (j % kPage);
+      const T* k = kc + row * hd;
       float dot = 0.f;
       for (int d = 0; d < hd; ++d) dot = fmaf(q_s[warp][d], to_float(k[d]), dot);
       sc = dot * scale;
@@ -164,15 +188,15 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
     l = l * corr + warp_sum(pj);
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= corr;
-    const int n_valid = min(32, p - base + 1);
+    const int n_valid = min(32, n_keys - base);
     for (int jj = 0; jj < n_valid; ++jj) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const unsigned long long r = __shfl_sync(0xffffffffu, (unsigned long long)row, jj);
-      const T* v = vc + r;
+      const T* v = vc + r * vd;
 #pragma unroll
       for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < hd) acc[i] = fmaf(pv, to_float(v[d]), acc[i]);
+        if (d < vd) acc[i] = fmaf(pv, to_float(v[d]), acc[i]);
       }
     }
     m = m_new;
@@ -181,29 +205,45 @@ attention_plain_kernel(const T* __restrict__ qkv, const T* __restrict__ kc, cons
 #pragma unroll
   for (int i = 0; i < kMaxHeadDim / 32; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) o[d] = from_float<T>(acc[i] * inv);
+    if (d < vd) o[d] = from_float<T>(acc[i] * inv);
   }
 }
+
+EMBER_API int ember_attention_plain_v(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                      const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                      int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                                      int dtype, cudaStream_t stream);
 
 EMBER_API int ember_attention_plain(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
                                     const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
                                     int n_heads, int kv_heads, int hd, float scale, int window, int dtype,
                                     cudaStream_t stream) {
+  return ember_attention_plain_v(qkv, kc, vc, out, positions, token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads,
+                                 hd, scale, window, hd, 0, dtype, stream);
+}
+
+// The same with values of `vd` per head and the first `keep_first` positions of a sequence visible beside the
+// window: query p sees key j <= p if p - j < window or j < keep_first (window 0: all keys).
+EMBER_API int ember_attention_plain_v(const void* qkv, const void* kc, const void* vc, void* out, const int* positions,
+                                      const int* token_seq, const int* seq_slot, const int* pages, int max_blocks, int T,
+                                      int n_heads, int kv_heads, int hd, float scale, int window, int vd, int keep_first,
+                                      int dtype, cudaStream_t stream) {
   EMBER_CHECK(T > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
   EMBER_CHECK(hd >= 1 && hd <= kMaxHeadDim, "attention: head size %d is not in [1, %d]", hd, kMaxHeadDim);
-  EMBER_CHECK(window >= 0, "attention: window %d", window);
+  EMBER_CHECK(vd >= 1 && vd <= kMaxHeadDim, "attention: value size %d is not in [1, %d]", vd, kMaxHeadDim);
+  EMBER_CHECK(window >= 0 && keep_first >= 0, "attention: window %d, kept first %d", window, keep_first);
   const long long items = (long long)T * n_heads;
   const int grid = (int)((items + 3) / 4);
   if (dtype == EMBER_F32)
     attention_plain_kernel<float><<<grid, 128, 0, stream>>>((const float*)qkv, (const float*)kc, (const float*)vc,
                                                             (float*)out, positions, token_seq, seq_slot, pages,
-                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window);
+                                                            max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first);
   else if (dtype == EMBER_BF16)
     attention_plain_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>(
         (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, positions,
-        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window);
+        token_seq, seq_slot, pages, max_blocks, T, n_heads, kv_heads, hd, scale, window, vd, keep_first);
   else
     return ember_fail("attention: element type %d", dtype);
   EMBER_LAUNCH_OK("attention_plain");

@@ -7,7 +7,9 @@
 // block takes 64 consecutive new tokens of one (sequence, head); each of its 4 warps owns 16 query
 // rows; key blocks are the cache's 64-position pages, brought in with cp.async into a double
 // buffer while the previous page is used.  The keys of a page beyond a query's position (or before
-// its window) are masked by selection, never by arithmetic on what the page holds.
+// its window) are masked by selection, never by arithmetic on what the page holds.  With
+// `keep_first` > 0 the first positions of a sequence stay visible beside the window: the pages that
+// hold them and lie before the window's first page are taken first, then the window's pages.
 //
 // Head sizes: multiples of 16 up to 128 (one instantiation each); larger heads take the plain
 // kernel.
@@ -67,7 +69,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                          const int* __restrict__ seq_new, const int* __restrict__ cu_new,
                          const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, float scale_log2,
-                         int window) {
+                         int window, int keep_first) {
   constexpr int LD = HD + 8, KS = HD / 16;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
@@ -93,14 +95,18 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
   const int p_last = p0 + rows - 1;
   const int kb_first = window > 0 ? max(0, p0 - window + 1) / kRows : 0;
   const int kb_last = p_last / kRows;
+  // pages of kept first positions before the window's first page, and the trips of the page loop
+  const int n_kept = window > 0 ? min((keep_first + kRows - 1) / kRows, kb_first) : 0;
+  const int n_trips = n_kept + kb_last - kb_first + 1;
+  auto block_of = [&](int trip) { return trip < n_kept ? trip : kb_first + trip - n_kept; };
   const int kvh = h / (n_heads / kv_heads);
   const size_t qkv_width = (size_t)(n_heads + 2 * kv_heads) * HD;
   const int* my_pages = pages + (size_t)s * max_blocks;
   auto page_base = [&](int kb) { return ((size_t)max(my_pages[kb], 0) * kv_heads + kvh) * kRows * HD; };
 
   load_tile<HD>(sQ, qkv + (size_t)tok0 * qkv_width + (size_t)h * HD, qkv_width, rows);
-  load_tile<HD>(sK, kc + page_base(kb_first), HD, kRows);
-  load_tile<HD>(sV, vc + page_base(kb_first), HD, kRows);
+  load_tile<HD>(sK, kc + page_base(block_of(0)), HD, kRows);
+  load_tile<HD>(sV, vc + page_base(block_of(0)), HD, kRows);
   cp_async_commit();
 
   unsigned qf[KS][4];
@@ -112,18 +118,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   const int row_pos[2] = {p0 + warp * 16 + g, p0 + warp * 16 + g + 8};  // positions of this thread's two rows
 
-  for (int kb = kb_first; kb <= kb_last; ++kb) {
-    const int buf = (kb - kb_first) & 1;
-    if (kb + 1 <= kb_last) {
-      load_tile<HD>(sK + (buf ^ 1) * kRows * LD, kc + page_base(kb + 1), HD, kRows);
-      load_tile<HD>(sV + (buf ^ 1) * kRows * LD, vc + page_base(kb + 1), HD, kRows);
+  for (int trip = 0; trip < n_trips; ++trip) {
+    const int kb = block_of(trip);
+    const int buf = trip & 1;
+    if (trip + 1 < n_trips) {
+      load_tile<HD>(sK + (buf ^ 1) * kRows * LD, kc + page_base(block_of(trip + 1)), HD, kRows);
+      load_tile<HD>(sV + (buf ^ 1) * kRows * LD, vc + page_base(block_of(trip + 1)), HD, kRows);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (kb == kb_first) {
+    if (trip == 0) {
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks)
         ldmatrix_x4(qf[ks], sQ + (warp * 16 + (lane & 15)) * LD + ks * 16 + (lane >> 4) * 8);
@@ -150,7 +157,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
 
     // mask by selection where the page crosses a query's position or its window's start
     const int key0 = kb * kRows;
-    const bool need_mask = key0 + kRows - 1 > p0 + warp * 16 || (window > 0 && key0 < p_last - window + 1);
+    const bool need_mask = key0 + kRows - 1 > p0 + warp * 16 || (window > 0 && key0 < p_last - window + 1);  // (kept pages too)
     if (need_mask) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
@@ -158,7 +165,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
         for (int j = 0; j < 4; ++j) {
           const int key = key0 + i * 8 + c2 + (j & 1);
           const int pos = row_pos[j >> 1];
-          const bool seen = key <= pos && (window <= 0 || key > pos - window);
+          const bool seen = key <= pos && (window <= 0 || key > pos - window || key < keep_first);
           if (!seen) sc[i][j] = -INFINITY;
         }
     }
@@ -242,7 +249,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloa
 template <int HD>
 int launch(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot, const int* seq_start,
            const int* seq_new, const int* cu_new, const int* pages, int max_blocks, int n_seqs, int max_new,
-           int n_heads, int kv_heads, float scale, int window, cudaStream_t stream) {
+           int n_heads, int kv_heads, float scale, int window, int keep_first, cudaStream_t stream) {
   const int smem = 5 * kRows * (HD + 8) * (int)sizeof(__nv_bfloat16);
   static bool configured = false;  // per instantiation
   if (!configured) {
@@ -253,12 +260,17 @@ int launch(const void* qkv, const void* kc, const void* vc, void* out, const int
   dim3 grid((max_new + kRows - 1) / kRows, n_heads, n_seqs);
   attention_prefill_kernel<HD><<<grid, kThreads, smem, stream>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, (__nv_bfloat16*)out, seq_slot,
-      seq_start, seq_new, cu_new, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window);
+      seq_start, seq_new, cu_new, pages, max_blocks, n_heads, kv_heads, scale * 1.4426950408889634f, window, keep_first);
   EMBER_LAUNCH_OK("attention_prefill");
   return 0;
 }
 
 }  // namespace
+
+EMBER_API int ember_attention_prefill_kept(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
+                                           const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
+                                           int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
+                                           float scale, int window, int keep_first, cudaStream_t stream);
 
 // Returns 0 on success, 1 on an error, 2 if this head size has no tensor-core instantiation (the
 // caller then takes the plain kernel).
@@ -266,6 +278,15 @@ EMBER_API int ember_attention_prefill(const void* qkv, const void* kc, const voi
                                       const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
                                       int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
                                       float scale, int window, cudaStream_t stream) {
+  return ember_attention_prefill_kept(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs,
+                                      max_new, n_heads, kv_heads, hd, scale, window, 0, stream);
+}
+
+// The same with the first `keep_first` positions of every sequence visible beside the window.
+EMBER_API int ember_attention_prefill_kept(const void* qkv, const void* kc, const void* vc, void* out, const int* seq_slot,
+                                           const int* seq_start, const int* seq_new, const int* cu_new, const int* pages,
+                                           int max_blocks, int n_seqs, int max_new, int n_heads, int kv_heads, int hd,
+                                           float scale, int window, int keep_first, cudaStream_t stream) {
   EMBER_CHECK(n_seqs > 0 && max_new > 0 && n_heads > 0 && kv_heads > 0 && max_blocks > 0, "attention_prefill: bad sizes");
   EMBER_CHECK(n_heads % kv_heads == 0, "attention_prefill: %d heads are not a multiple of %d key/value heads", n_heads,
               kv_heads);
@@ -273,12 +294,12 @@ EMBER_API int ember_attention_prefill(const void* qkv, const void* kc, const voi
               hd);
   EMBER_CHECK(n_seqs <= 65535 && n_heads <= 65535, "attention_prefill: %d sequences x %d heads exceed one launch", n_seqs,
               n_heads);
-  EMBER_CHECK(window >= 0, "attention_prefill: window %d", window);
+  EMBER_CHECK(window >= 0 && keep_first >= 0, "attention_prefill: window %d, kept first %d", window, keep_first);
   EMBER_CHECK(scale > 0.f, "attention_prefill: scale %g is not positive", (double)scale);
 #define EMBER_PREFILL(HD)                                                                                           \
   case HD:                                                                                                          \
     return launch<HD>(qkv, kc, vc, out, seq_slot, seq_start, seq_new, cu_new, pages, max_blocks, n_seqs, max_new,   \
-                      n_heads, kv_heads, scale, window, stream)
+                      n_heads, kv_heads, scale, window, keep_first, stream)
   switch (hd) {
     EMBER_PREFILL(16);
     EMBER_PREFILL(32);

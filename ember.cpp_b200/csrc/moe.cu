@@ -1,0 +1,323 @@
+// Experts chosen by a table: the step's (token, choice) pairs sorted by expert, and the two grouped
+// products that run every expert over its own pairs.
+//
+// Pair q = t * top + k is choice k of token t; its expert is table[token id][k].  `moe_route` makes,
+// in one launch, the pairs' experts, each expert's count as a running sum (offsets[experts + 1]) and the
+// pairs in expert order (sorted[pairs]; the order inside an expert is whatever the atomics gave, which no
+// result depends on: every pair's row is computed by itself).  The products:
+//   gate_up   inner[q, :] = silu(Wg_e a_t) * (Wu_e a_t)     (W_e = [gate | up] stacked, [2 * inner, width])
+//   down      y[q, :]     = Wd_e inner[q, :]                (float32)
+// Few pairs (a decode step): a warp per output value streams the expert's rows once, which is all the
+// traffic there is.  Many pairs (a prompt): tiles of 64 pairs x 64 outputs of one expert on mma.sync
+// m16n8k16 with cp.async double buffering.  float32 takes the streaming form at every size: one
+// fixed order of additions per output value, no reduced-precision matrix mode.
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------- routing
+__global__ void __launch_bounds__(1024)
+moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int n_pairs, int top, int experts,
+                 int vocab, int* __restrict__ pair_expert, int* __restrict__ offsets, int* __restrict__ sorted) {
+  extern __shared__ int sm_i[];  // count[experts], cursor[experts]
+  int* count = sm_i;
+  int* cursor = sm_i + experts;
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int q = threadIdx.x; q < n_pairs; q += blockDim.x) {
+    int tok = tokens[q / top];
+    tok = min(max(tok, 0), vocab - 1);
+    int e = table[(size_t)tok * top + q % top];
+    e = min(max(e, 0), experts - 1);
+    pair_expert[q] = e;
+    atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts; ++e) {
+      offsets[e] = run;
+      cursor[e] = run;
+      run += count[e];
+    }
+    offsets[experts] = run;
+  }
+  __syncthreads();
+  for (int q = threadIdx.x; q < n_pairs; q += blockDim.x) sorted[atomicAdd(&cursor[pair_expert[q]], 1)] = q;
+}
+
+// ---------------------------------------------------------------------------- streaming form
+// The dot product of two rows of K values by one warp: lanes take 16-byte pieces in turn where the rows
+// allow it, single values else; the lanes' sums are added by warp_sum.  The order depends on K alone.
+template <typename T>
+__device__ __forceinline__ float warp_dot(const T* __restrict__ w, const T* a, int K, int lane) {
+  constexpr int V = 16 / (int)sizeof(T);
+  float acc = 0.f;
+  if (K % V == 0) {
+    for (int k = lane * V; k < K; k += 32 * V) {
+      const uint4 wr = *reinterpret_cast<const uint4*>(w + k);
+      const uint4 ar = __ldcg(reinterpret_cast<const uint4*>(a + k));
+      const T* wv = reinterpret_cast<const T*>(&wr);
+      const T* av = reinterpret_cast<const T*>(&ar);
+#pragma unroll
+      for (int i = 0; i < V; ++i) acc = fmaf(to_float(wv[i]), to_float(av[i]), acc);
+    }
+  } else {
+    for (int k = lane; k < K; k += 32) acc = fmaf(to_float(w[k]), to_float(__ldcg(a + k)), acc);
+  }
+  return warp_sum(acc);
+}
+
+constexpr int kStreamWarps = 8;
+constexpr int kStreamOutputs = 4;  // per warp
+
+// grid (pairs, ceil(inner / 32))
+template <typename T>
+__global__ void __launch_bounds__(kStreamWarps * 32)
+moe_gate_up_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ pair_expert,
+                          T* __restrict__ out, int top, int width, int inner) {
+  const int q = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* row = a + (size_t)(q / top) * width;
+  const T* we = w + (size_t)pair_expert[q] * 2 * inner * width;
+  for (int i = 0; i < kStreamOutputs; ++i) {
+    const int f = (blockIdx.y * kStreamWarps + warp) * kStreamOutputs + i;
+    if (f >= inner) return;
+    const float g = warp_dot(we + (size_t)f * width, row, width, lane);
+    const float u = warp_dot(we + (size_t)(inner + f) * width, row, width, lane);
+    if (lane == 0) out[(size_t)q * inner + f] = from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+// grid (pairs, ceil(width / 32))
+template <typename T>
+__global__ void __launch_bounds__(kStreamWarps * 32)
+moe_down_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ pair_expert,
+                       float* __restrict__ out, int width, int inner) {
+  const int q = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const T* row = a + (size_t)q * inner;
+  const T* we = w + (size_t)pair_expert[q] * width * inner;
+  for (int i = 0; i < kStreamOutputs; ++i) {
+    const int n = (blockIdx.y * kStreamWarps + warp) * kStreamOutputs + i;
+    if (n >= width) return;
+    const float v = warp_dot(we + (size_t)n * inner, row, inner, lane);
+    if (lane == 0) out[(size_t)q * width + n] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------- tiled form (bfloat16)
+constexpr int kTile = 64;   // pairs a tile, and outputs a tile
+constexpr int kStep = 32;   // of the summed dimension per trip
+constexpr int kLd = kStep + 8;
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned dst = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// GATED: W_e = [gate | up] of n_out rows each, the result silu(gate) * up in bfloat16 and the input rows are
+// the tokens' (pair / top); else W_e has n_out rows, the result is float32 and the input rows are the pairs'.
+// grid (tiles of pairs: an upper bound, ceil(n_out / 64)); a block finds its expert and its tile of that
+// expert's pairs from the offsets, and leaves if there is none.
+template <bool GATED>
+__global__ void __launch_bounds__(128)
+moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
+                const int* __restrict__ sorted, void* __restrict__ out, int experts, int top, int K, int n_out) {
+  constexpr int NW = GATED ? 2 : 1;
+  __shared__ __align__(16) __nv_bfloat16 sA[2][kTile * kLd];
+  __shared__ __align__(16) __nv_bfloat16 sW[2][NW][kTile * kLd];
+  __shared__ int s_rows[kTile];  // the input row of each of the tile's pairs, -1 past the expert's last
+  __shared__ int s_pair[kTile];
+  __shared__ int s_expert;
+
+  if (threadIdx.x == 0) {
+    int tile = blockIdx.x, found = -1;
+    for (int e = 0; e < experts; ++e) {
+      const int tiles = (offsets[e + 1] - offsets[e] + kTile - 1) / kTile;
+      if (tile < tiles) {
+        found = e;
+        break;
+      }
+      tile -= tiles;
+    }
+    s_expert = found;
+    s_pair[0] = tile;  // (handed to the others below)
+  }
+  __syncthreads();
+  const int e = s_expert;
+  if (e < 0) return;
+  const int tile = s_pair[0];
+  __syncthreads();
+  const int first = offsets[e] + tile * kTile, count = min(kTile, offsets[e + 1] - first);
+  if ((int)threadIdx.x < kTile) {
+    const int q = (int)threadIdx.x < count ? sorted[first + threadIdx.x] : -1;
+    s_pair[threadIdx.x] = q;
+    s_rows[threadIdx.x] = q < 0 ? -1 : (GATED ? q / top : q);
+  }
+  __syncthreads();
+
+  const int n0 = blockIdx.y * kTile;
+  const __nv_bfloat16* we = w + (size_t)e * NW * n_out * K;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  auto load = [&](int buf, int k0) {
+    constexpr int CPR = kStep / 8;  // 16-byte pieces a row
+    for (int id = threadIdx.x; id < kTile * CPR; id += 128) {
+      const int r = id / CPR, c = id % CPR;
+      const bool in_k = k0 + c * 8 < K;
+      const int src = s_rows[r];
+      const bool ok_a = src >= 0 && in_k;
+      cp_async_16(&sA[buf][r * kLd + c * 8], a + (ok_a ? (size_t)src * K + k0 + c * 8 : 0), ok_a);
+      const bool ok_w = n0 + r < n_out && in_k;
+#pragma unroll
+      for (int m = 0; m < NW; ++m)
+        cp_async_16(&sW[buf][m][r * kLd + c * 8], we + (ok_w ? ((size_t)m * n_out + n0 + r) * K + k0 + c * 8 : 0), ok_w);
+    }
+  };
+
+  float acc[NW][8][4];
+#pragma unroll
+  for (int m = 0; m < NW; ++m)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[m][i][j] = 0.f;
+
+  const int trips = (K + kStep - 1) / kStep;
+  load(0, 0);
+  cp_async_commit();
+  for (int trip = 0; trip < trips; ++trip) {
+    const int buf = trip & 1;
+    if (trip + 1 < trips) {
+      load(buf ^ 1, (trip + 1) * kStep);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < kStep / 16; ++ks) {
+      unsigned af[4];
+      ldmatrix_x4(af, &sA[buf][(warp * 16 + (lane & 15)) * kLd + ks * 16 + (lane >> 4) * 8]);
+#pragma unroll
+      for (int m = 0; m < NW; ++m) {
+#pragma unroll
+        for (int np = 0; np < 4; ++np) {
+          unsigned b[4];
+          ldmatrix_x4(b, &sW[buf][m][(np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + ks * 16 + ((lane >> 3) & 1) * 8]);
+          mma_bf16(acc[m][2 * np], af, b[0], b[1]);
+          mma_bf16(acc[m][2 * np + 1], af, b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();  // the other buffer is refilled at the top of the next trip
+  }
+
+  const int g = lane >> 2, c2 = (lane & 3) * 2;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    const int q = s_pair[warp * 16 + g + r * 8];
+    if (q < 0) continue;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + i * 8 + c2 + j;
+        if (n >= n_out) continue;
+        if constexpr (GATED) {
+          const float gv = acc[0][i][2 * r + j], uv = acc[1][i][2 * r + j];
+          static_cast<__nv_bfloat16*>(out)[(size_t)q * n_out + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+        } else {
+          static_cast<float*>(out)[(size_t)q * n_out + n] = acc[0][i][2 * r + j];
+        }
+      }
+    }
+  }
+}
+
+}  // namespace
+
+// tokens [T] (ids), table [vocab, top]; pair_expert [T * top], offsets [experts + 1], sorted [T * top]
+EMBER_API int ember_moe_route(const int* tokens, const int* table, int T, int top, int experts, int vocab, int* pair_expert,
+                              int* offsets, int* sorted, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && vocab > 0 && top <= experts, "moe_route: bad sizes");
+  EMBER_CHECK(experts <= 4096, "moe_route: %d experts (at most 4096)", experts);
+  EMBER_CHECK((long long)T * top < (1ll << 30), "moe_route: %d tokens x %d choices", T, top);
+  moe_route_kernel<<<1, 1024, 2 * experts * sizeof(int), stream>>>(tokens, table, T * top, top, experts, vocab,
+                                                                   pair_expert, offsets, sorted);
+  EMBER_LAUNCH_OK("moe_route");
+  return 0;
+}
+
+// a [T, width] (dtype), w [experts, 2 * inner, width], out [T * top, inner] (dtype).  tiled != 0 (bfloat16 only):
+// the tensor-core tiles; else the streaming form.
+EMBER_API int ember_moe_gate_up(const void* a, const void* w, const int* pair_expert, const int* offsets, const int* sorted,
+                                void* out, int T, int top, int experts, int width, int inner, int tiled, int dtype,
+                                cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && width > 0 && inner > 0, "moe_gate_up: bad sizes");
+  const long long pairs = (long long)T * top;
+  if (tiled) {
+    EMBER_CHECK(dtype == EMBER_BF16 && width % 8 == 0, "moe_gate_up: tiles take bfloat16 rows that are multiples of 8");
+    const dim3 grid((unsigned)((pairs + kTile - 1) / kTile + experts), (inner + kTile - 1) / kTile);
+    EMBER_CHECK(grid.y <= 65535, "moe_gate_up: %d outputs exceed one launch", inner);
+    moe_tile_kernel<true><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, offsets, sorted, out,
+                                                    experts, top, width, inner);
+    EMBER_LAUNCH_OK("moe_gate_up");
+    return 0;
+  }
+  const dim3 grid((unsigned)pairs, (inner + kStreamWarps * kStreamOutputs - 1) / (kStreamWarps * kStreamOutputs));
+  EMBER_CHECK(grid.y <= 65535, "moe_gate_up: %d outputs exceed one launch", inner);
+  if (dtype == EMBER_F32)
+    moe_gate_up_stream_kernel<float><<<grid, kStreamWarps * 32, 0, stream>>>((const float*)a, (const float*)w, pair_expert,
+                                                                            (float*)out, top, width, inner);
+  else if (dtype == EMBER_BF16)
+    moe_gate_up_stream_kernel<__nv_bfloat16><<<grid, kStreamWarps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, pair_expert, (__nv_bfloat16*)out, top, width, inner);
+  else
+    return ember_fail("moe_gate_up: element type %d", dtype);
+  EMBER_LAUNCH_OK("moe_gate_up");
+  return 0;
+}
+
+// a [T * top, inner] (dtype), w [experts, width, inner], out float32 [T * top, width]
+EMBER_API int ember_moe_down(const void* a, const void* w, const int* pair_expert, const int* offsets, const int* sorted,
+                             float* out, int T, int top, int experts, int width, int inner, int tiled, int dtype,
+                             cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && top > 0 && experts > 0 && width > 0 && inner > 0, "moe_down: bad sizes");
+  const long long pairs = (long long)T * top;
+  if (tiled) {
+    EMBER_CHECK(dtype == EMBER_BF16 && inner % 8 == 0, "moe_down: tiles take bfloat16 rows that are multiples of 8");
+    const dim3 grid((unsigned)((pairs + kTile - 1) / kTile + experts), (width + kTile - 1) / kTile);
+    EMBER_CHECK(grid.y <= 65535, "moe_down: %d outputs exceed one launch", width);
+    moe_tile_kernel<false><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, offsets, sorted, out,
+                                                     experts, top, inner, width);
+    EMBER_LAUNCH_OK("moe_down");
+    return 0;
+  }
+  const dim3 grid((unsigned)pairs, (width + kStreamWarps * kStreamOutputs - 1) / (kStreamWarps * kStreamOutputs));
+  EMBER_CHECK(grid.y <= 65535, "moe_down: %d outputs exceed one launch", width);
+  if (dtype == EMBER_F32)
+    moe_down_stream_kernel<float><<<grid, kStreamWarps * 32, 0, stream>>>((const float*)a, (const float*)w, pair_expert, out,
+                                                                         width, inner);
+  else if (dtype == EMBER_BF16)
+    moe_down_stream_kernel<__nv_bfloat16><<<grid, kStreamWarps * 32, 0, stream>>>(
+        (const __nv_bfloat16*)a, (const __nv_bfloat16*)w, pair_expert, out, width, inner);
+  else
+    return ember_fail("moe_down: element type %d", dtype);
+  EMBER_LAUNCH_OK("moe_down");
+  return 0;
+}

@@ -55,6 +55,26 @@ _SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_attention_prefill_tc": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_rmsnorm": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+    "ember_add_normed": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_float, _c_void],
+    "ember_gated_act": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void],
+    "ember_gated_group_norm": [_c_void, _c_void, ctypes.c_longlong, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float,
+                               _c_int, _c_void],
+    "ember_kv_store_v": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_int, _c_int, _c_void],
+    "ember_attention_plain_v": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_attention_prefill_kept": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                                     _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
+    "ember_conv_silu": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
+                        _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_ssd_scan": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                       _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_moe_route": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
+    "ember_moe_gate_up": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
+                          _c_int, _c_int, _c_void],
+    "ember_moe_down": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
 }
 
@@ -63,6 +83,7 @@ class KernelError(RuntimeError):
     pass
 
 
+MOE_TILE_PAIRS = 48   # (token, choice) pairs from which the experts' products take tensor-core tiles (bfloat16)
 SMALL_M = 16          # rows up to which the mma.sync weight-streaming product (linear_decode.cu) is used
 STREAM_M = 64         # rows up to which the tcgen05 weight-streaming product (linear_stream.cu) is used above that
 TC_MIN_M = 64         # rows above which the tcgen05 product is used (its tiles have 128 rows)
@@ -475,13 +496,17 @@ class CudaOps:
     def clear_tails(self, group, tails) -> None:
         """Zeroes, in every key and value tensor of a cache group, the rows from `row` on of each page
         named in tails [n, 2] = (page, row) (page < 0: nothing)."""
-        table = getattr(group, "_tensor_table", None)
-        if table is None:      # the addresses of the group's tensors, once
-            tensors = list(group.k) + list(group.v)
-            table = group._tensor_table = torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=tensors[0].device)
         need = group.need
-        self._call("ember_clear_tails", table.data_ptr(), table.numel(), tails.data_ptr(), tails.shape[0], need.kv_heads,
-                   need.head_dim, group.k[0].element_size())
+        tables = getattr(group, "_tensor_tables", None)
+        if tables is None:      # the addresses of the group's tensors, once (keys and values apart where their rows differ)
+            sets = [(list(group.k) + list(group.v), need.head_dim)] if need.v_dim == need.head_dim else \
+                [(list(group.k), need.head_dim), (list(group.v), need.v_dim)]
+            tables = group._tensor_tables = [
+                (torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=tensors[0].device), row)
+                for tensors, row in sets]
+        for table, row in tables:
+            self._call("ember_clear_tails", table.data_ptr(), table.numel(), tails.data_ptr(), tails.shape[0], need.kv_heads,
+                       row, group.k[0].element_size())
 
     def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
         if qkv.dtype != cache.k.dtype:
@@ -491,15 +516,22 @@ class CudaOps:
                    plan.pages[cache.group_index].data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
                    _code(qkv.dtype))
 
-    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False):
+    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False,
+                  keep_first=None, value_dim=None):
         """Causal attention of the step's tokens over the cache.  With `store` their own keys and
         values are written into the cache first (in the same launch where a kernel can).
         float32: the plain kernel, whose sums depend on positions alone.  bfloat16: one token per
         sequence takes the split decode kernel; anything else the tensor-core prefill kernel, or
-        the plain kernel for head sizes that one has no instantiation for."""
+        the plain kernel for head sizes that one has no instantiation for.
+        keep_first / value_dim (a mixer that keeps a sequence's first positions visible beside its
+        window, or whose values have a row size of their own): the plain kernel, which knows both and
+        every head size, or for prompts in bfloat16 the mma.sync kernel where it has the head size."""
         if qkv.dtype != cache.k.dtype or out_dtype != qkv.dtype:
             raise KernelError("attention: activations, cache and output have one element type")
         self._dense(qkv, "qkv")
+        if keep_first is not None or value_dim is not None:
+            return self._attention_kept(qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store,
+                                        int(keep_first or 0), head_dim if value_dim is None else int(value_dim))
         out = torch.empty((plan.T, n_heads * head_dim), dtype=out_dtype, device=qkv.device)
         pages = plan.pages[cache.group_index]
         if qkv.dtype == torch.bfloat16 and plan.all_single:
@@ -551,6 +583,157 @@ class CudaOps:
                    out.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(),
                    pages.data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, head_dim,
                    float(scale), int(window), _code(qkv.dtype))
+        return out
+
+    def _attention_kept(self, qkv, cache, plan, n_heads, kv_heads, hd, scale, window, out_dtype, store, keep_first, vd):
+        if qkv.shape[1] != (n_heads + kv_heads) * hd + kv_heads * vd:
+            raise KernelError(f"attention: rows of {qkv.shape[1]} values are not q | k | v of {n_heads} x {hd}, "
+                              f"{kv_heads} x {hd} and {kv_heads} x {vd}")
+        if tuple(cache.v.shape[1:]) != (kv_heads, 64, vd) or tuple(cache.k.shape[1:]) != (kv_heads, 64, hd):
+            raise KernelError("attention: the cache's pages do not have the mixer's head sizes")
+        out = torch.empty((plan.T, n_heads * vd), dtype=out_dtype, device=qkv.device)
+        pages = plan.pages[cache.group_index]
+        if store:
+            self._call("ember_kv_store_v", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), plan.positions.data_ptr(),
+                       plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.T,
+                       n_heads, kv_heads, hd, vd, _code(qkv.dtype))
+        if qkv.dtype == torch.bfloat16 and vd == hd and scale > 0 and not plan.all_single:
+            rc = self._call("ember_attention_prefill_kept", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                            out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
+                            plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n, plan.max_new, n_heads,
+                            kv_heads, hd, float(scale), int(window), keep_first, allow=(2,))
+            if rc == 0:
+                return out
+        self._call("ember_attention_plain_v", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), out.data_ptr(),
+                   plan.positions.data_ptr(), plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(),
+                   plan.max_blocks, plan.T, n_heads, kv_heads, hd, float(scale), int(window), vd, keep_first,
+                   _code(qkv.dtype))
+        return out
+
+    # ------------------------------------------------------------------ RMS norm, gates
+    def rmsnorm(self, x, w, eps, out_dtype, offset=0.0):
+        """x / sqrt(mean(x^2) + eps) * (offset + w) of float32 rows."""
+        rows, d = x.shape
+        if x.dtype != torch.float32 or w.dtype != torch.float32 or w.shape[0] != d:
+            raise KernelError("rmsnorm: float32 rows and a float32 gain of their width")
+        out = torch.empty((rows, d), dtype=out_dtype, device=x.device)
+        self._call("ember_rmsnorm", self._dense(x, "rmsnorm input").data_ptr(), w.data_ptr(), out.data_ptr(), rows, d,
+                   float(eps), float(offset), _code(out_dtype))
+        return out
+
+    def add_normed(self, x, branches, w, eps, offset=0.0):
+        """x += rmsnorm(sum of factor * rows over `branches`) in place, one launch.  Every branch is float32
+        [rows, width]; its rows may lie apart (a slice of a wider tensor), their values may not."""
+        rows, d = x.shape
+        if x.dtype != torch.float32 or not x.is_contiguous() or w.dtype != torch.float32 or w.shape[0] != d:
+            raise KernelError("add_normed: a contiguous float32 stream and a float32 gain of its width")
+        n = len(branches)
+        if not 1 <= n <= 16:
+            raise KernelError(f"add_normed: {n} branches (1 to 16)")
+        for t, _ in branches:
+            if t.dtype != torch.float32 or tuple(t.shape) != (rows, d) or t.stride(1) != 1 or not t.is_cuda:
+                raise KernelError("add_normed: every branch is float32 [rows, width] with contiguous rows")
+        ptrs = (_c_void * n)(*[t.data_ptr() for t, _ in branches])
+        strides = (ctypes.c_longlong * n)(*[t.stride(0) for t, _ in branches])
+        factors = (_c_float * n)(*[float(f) for _, f in branches])
+        self._call("ember_add_normed", x.data_ptr(), ctypes.cast(ptrs, _c_void), ctypes.cast(strides, _c_void),
+                   ctypes.cast(factors, _c_void), n, w.data_ptr(), rows, d, float(eps), float(offset))
+        return x
+
+    _GATES = {"silu": 0, "clamped_sigmoid": 1}
+
+    def gated_act(self, gu, activation, limit=0.0, alpha=1.0, shift=0.0):
+        """Rows of [gate | up] -> act(gate) * up, see parts/mlp.py for the two forms."""
+        if activation not in self._GATES:
+            raise KernelError(f"gated_act: activation {activation!r}")
+        rows, n2 = gu.shape
+        if n2 % 2:
+            raise KernelError("gated_act: rows of gate | up have an even length")
+        out = torch.empty((rows, n2 // 2), dtype=gu.dtype, device=gu.device)
+        self._call("ember_gated_act", self._dense(gu, "gate | up").data_ptr(), out.data_ptr(), rows, n2 // 2,
+                   self._GATES[activation], float(limit), float(alpha), float(shift), _code(gu.dtype))
+        return out
+
+    # ------------------------------------------------------------------ Mamba-2
+    def conv_silu(self, proj, col0, channels, conv_w, conv_b, conv_state, plan):
+        """silu of the causal convolution (conv_w [channels, taps], the last tap on the current token) of
+        `channels` columns from col0 of `proj`, per sequence of the step; conv_state [slots, taps - 1, channels]
+        float32 carries the rows before the step and is advanced."""
+        taps = conv_w.shape[1]
+        if conv_w.shape[0] != channels or conv_b.shape[0] != channels or col0 + channels > proj.shape[1]:
+            raise KernelError("conv_silu: the filter, its bias and the columns do not fit")
+        if taps > 1 and (conv_state is None or tuple(conv_state.shape[1:]) != (taps - 1, channels) or conv_state.dtype != torch.float32):
+            raise KernelError("conv_silu: the state is float32 [slots, taps - 1, channels]")
+        self._dense(proj, "conv input")
+        out = torch.empty((plan.T, channels), dtype=proj.dtype, device=proj.device)
+        self._call("ember_conv_silu", proj.data_ptr(), proj.stride(0), int(col0), int(channels), int(taps), conv_w.data_ptr(),
+                   conv_b.data_ptr(), self._ptr(conv_state), out.data_ptr(), plan.token_seq.data_ptr(),
+                   plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.T, plan.n,
+                   1 if plan.all_single else 0, _code(proj.dtype))
+        return out
+
+    def ssd_scan(self, xbc, proj, dt_col, dt_bias, a_log, skip, state, plan, heads, vdim, groups, n_state):
+        """The recurrence of parts/ssm.py over the step's sequences: xbc [T, x | B | C], the raw step sizes in
+        `heads` columns from dt_col of `proj`, state float32 [slots, heads, vdim, n_state] (advanced); float32 y."""
+        inner = heads * vdim
+        if xbc.shape[1] != inner + 2 * groups * n_state or xbc.dtype != proj.dtype:
+            raise KernelError("ssd_scan: rows of x | B | C in the projection's element type")
+        if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, vdim, n_state):
+            raise KernelError("ssd_scan: the state is float32 [slots, heads, vdim, states]")
+        self._dense(xbc, "x | B | C")
+        y = torch.empty((plan.T, inner), dtype=torch.float32, device=xbc.device)
+        self._call("ember_ssd_scan", xbc.data_ptr(), proj.data_ptr(), proj.stride(0), int(dt_col), dt_bias.data_ptr(),
+                   a_log.data_ptr(), skip.data_ptr(), state.data_ptr(), y.data_ptr(), plan.seq_slot.data_ptr(),
+                   plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.n, heads, vdim, groups, n_state, _code(xbc.dtype))
+        return y
+
+    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype):
+        """unit(y * silu(z)) * w with the root mean square over each of `parts` equal pieces of a row; z: the
+        columns from z_col of `proj`."""
+        rows, n = y.shape
+        if y.dtype != torch.float32 or proj.dtype != out_dtype or z_col + n > proj.shape[1] or w.shape[0] != n:
+            raise KernelError("gated_group_norm: float32 y, the gate in the output's element type, a gain of y's width")
+        out = torch.empty((rows, n), dtype=out_dtype, device=y.device)
+        z = proj[:, z_col:]
+        self._call("ember_gated_group_norm", self._dense(y, "y").data_ptr(), z.data_ptr(), proj.stride(0), w.data_ptr(),
+                   out.data_ptr(), rows, n, int(parts), float(eps), _code(out_dtype))
+        return out
+
+    # ------------------------------------------------------------------ experts by table
+    def moe_route(self, tokens, T, table, experts, top):
+        """The step's (token, choice) pairs by expert: (expert of each pair, running counts, pairs in expert order)."""
+        pairs = T * top
+        buf = torch.empty(2 * pairs + experts + 1, dtype=torch.int32, device=table.device)
+        pair_expert, offsets, order = buf[:pairs], buf[pairs:pairs + experts + 1], buf[pairs + experts + 1:]
+        self._call("ember_moe_route", tokens.data_ptr(), table.data_ptr(), T, top, experts, table.shape[0],
+                   pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr())
+        return pair_expert, offsets, order, T, top, experts
+
+    def _moe_tiled(self, pairs, dtype, tiled):
+        if tiled is None:
+            tiled = dtype == torch.bfloat16 and pairs >= MOE_TILE_PAIRS
+        return 1 if tiled else 0
+
+    def moe_gate_up(self, h, w_gate_up, routing, out_dtype, tiled=None):
+        pair_expert, offsets, order, T, top, experts = routing
+        inner, width = w_gate_up.shape[1] // 2, w_gate_up.shape[2]
+        if h.dtype != w_gate_up.dtype or out_dtype != h.dtype or h.shape[1] != width or w_gate_up.shape[0] != experts:
+            raise KernelError("moe_gate_up: rows, stacked matrices and output of one element type and fitting sizes")
+        out = torch.empty((T * top, inner), dtype=out_dtype, device=h.device)
+        self._call("ember_moe_gate_up", self._dense(h, "rows").data_ptr(), self._dense(w_gate_up, "experts").data_ptr(),
+                   pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr(), out.data_ptr(), T, top, experts, width,
+                   inner, self._moe_tiled(T * top, h.dtype, tiled), _code(h.dtype))
+        return out
+
+    def moe_down(self, inner_rows, w_down, routing, tiled=None):
+        pair_expert, offsets, order, T, top, experts = routing
+        width, inner = w_down.shape[1], w_down.shape[2]
+        if inner_rows.dtype != w_down.dtype or tuple(inner_rows.shape) != (T * top, inner) or w_down.shape[0] != experts:
+            raise KernelError("moe_down: rows and stacked matrices of one element type and fitting sizes")
+        out = torch.empty((T, top, width), dtype=torch.float32, device=inner_rows.device)
+        self._call("ember_moe_down", self._dense(inner_rows, "rows").data_ptr(), self._dense(w_down, "experts").data_ptr(),
+                   pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr(), out.data_ptr(), T, top, experts, width,
+                   inner, self._moe_tiled(T * top, inner_rows.dtype, tiled), _code(inner_rows.dtype))
         return out
 
     # ------------------------------------------------------------------ sampling

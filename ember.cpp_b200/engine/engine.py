@@ -53,6 +53,10 @@ class Runtime:
     def table(self, t: torch.Tensor) -> torch.Tensor:
         return t.to(self.device).to(self.dtype).contiguous()
 
+    def index_table(self, t: torch.Tensor) -> torch.Tensor:
+        """Integer tables are read as int32 by every kernel."""
+        return t.to(self.device).to(torch.int32).contiguous()
+
     def vector(self, t: torch.Tensor) -> torch.Tensor:
         """Biases and norm parameters are read as float32 by every kernel."""
         return t.to(self.device).to(torch.float32).contiguous()
@@ -410,8 +414,11 @@ class _DecodeGraph:
         if dev.type != "cuda":
             self.graph = None
             return
-        # once without capture: libraries choose their algorithms and allocate outside the graph
+        # once without capture: libraries choose their algorithms and allocate outside the graph.  The step
+        # runs again when the graph is replayed, so what it changes for good (a recurrence's state) is put back.
+        saved = engine.cache.save_states([int(s) for s in host.packed[host.layout.seq_slot:host.layout.seq_slot + host.n]])
         engine.run(self.plan)
+        engine.cache.restore_states(saved)
         torch.cuda.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         before = engine.ops.launches

@@ -9,6 +9,9 @@ Roles and what each must provide:
   mixer     forward(ctx, h, residual, app) -> new residual stream    (h: normed input)
             cache_need() -> CacheNeed | None, state_need() -> StateNeed | {name: StateNeed} | None
   ffn       forward(ctx, h, residual) -> new residual stream
+            (mixer and ffn also: branches(ctx, h[, app]) -> [(float32 rows, factor)], the output as a weighted
+            sum that the caller adds itself, for arrangements that norm a sublayer's output before the sum;
+            a norm's add_normed(ctx, x, branches) makes that sum, norms it and adds it to the stream)
   position  embedding_table() -> tensor | None, max_positions() -> int | None,
             apply_qk(ctx, qkv, n_heads, kv_heads, head_dim) (in place; default: nothing)
   block     forward(ctx, x, app) -> x       (the arrangement of the four parts above)
@@ -33,15 +36,24 @@ class WeightSpec:
     mean: float = 0.0
     std: float = 0.02
     integer: bool = False     # an integer table (kept as int32); none in GPT-2
+    below: int = 0            # integer tables in random-weights mode: every row holds distinct values of [0, below)
 
 
 @dataclasses.dataclass(frozen=True)
 class CacheNeed:
-    """What a mixer wants from the cache: all keys (`full`) or the last `window` of them."""
+    """What a mixer wants from the cache: all keys (`full`) or the last `window` of them, with
+    the first `keep_first` positions of the sequence kept beside the window for good.  Values may
+    have a row size of their own (`value_dim`; 0: the keys')."""
     kind: str                 # "full" | "window"
     kv_heads: int
     head_dim: int
     window: int = 0
+    keep_first: int = 0
+    value_dim: int = 0
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
 
 @dataclasses.dataclass(frozen=True)
@@ -83,6 +95,15 @@ class Norm(Part):
     def forward(self, ctx, x, out_dtype):
         raise NotImplementedError
 
+    def add_normed(self, ctx, x, branches):
+        """x + norm(sum of factor * rows over `branches`), the sums in float32.  A norm whose kernel
+        does all of it in one launch overrides this."""
+        total = None
+        for rows, factor in branches:
+            term = rows.float() * factor
+            total = term if total is None else total + term
+        return x + self.forward(ctx, total.contiguous(), x.dtype)
+
 
 class Mixer(Part):
     role = "mixer"
@@ -96,12 +117,28 @@ class Mixer(Part):
     def forward(self, ctx, h, residual, app):
         raise NotImplementedError
 
+    def branches(self, ctx, h, app):
+        """The mixer's output as [(float32 rows [T, width], factor)]: the caller adds factor * rows.
+        The default runs forward() onto a stream of zeros."""
+        import torch
+        zero = torch.zeros((h.shape[0], self.width), dtype=torch.float32, device=h.device)
+        return [(self.forward(ctx, h, zero, app), 1.0)]
+
 
 class FeedForward(Part):
     role = "ffn"
+    # True for a feed-forward that reads the step's token ids (`ctx.plan.tokens`): the model then puts ids that
+    # a sampler left on the device into the step's description before the layers run
+    needs_tokens = False
 
     def forward(self, ctx, h, residual):
         raise NotImplementedError
+
+    def branches(self, ctx, h):
+        """As Mixer.branches."""
+        import torch
+        zero = torch.zeros((h.shape[0], self.width), dtype=torch.float32, device=h.device)
+        return [(self.forward(ctx, h, zero), 1.0)]
 
 
 class Position(Part):
@@ -120,7 +157,7 @@ class Position(Part):
 class Block(Part):
     role = "block"
 
-    def __init__(self, norm1: "Norm | None", mixer: Mixer, norm2: "Norm | None", ffn: FeedForward, **more_norms: Norm):
+    def __init__(self, norm1: "Norm | None", mixer: Mixer, norm2: "Norm | None", ffn: "FeedForward | None", **more_norms: Norm):
         super().__init__("")
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.more_norms = dict(more_norms)     # the arrangement's further norms, by the names the spec gives them
@@ -137,8 +174,8 @@ _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", 
 
 def register_part(role: str, kind: str, factory: Callable[..., Part]) -> None:
     """Makes `kind` available to specs for `role`.  `factory(prefix=..., **params)` builds the
-    part (for a block: `factory(norm1, mixer, norm2, ffn, **more_norms)`; a norm the spec leaves
-    out arrives as None)."""
+    part (for a block: `factory(norm1, mixer, norm2, ffn, **more_norms)`; a norm or a feed-forward
+    that the spec leaves out arrives as None)."""
     if role not in _REGISTRY:
         raise ValueError(f"unknown role {role!r}; roles: {sorted(_REGISTRY)}")
     _REGISTRY[role][kind] = factory

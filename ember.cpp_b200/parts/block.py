@@ -4,6 +4,12 @@
 sums in float32 (graph_ir.cpp:732-756, the sequential branch; operand order x then the
 branch's output, :754-756).  The mixer and the feed-forward add into the stream themselves so that
 their last projection can do the sum in its epilogue.
+
+`sandwich` norms every sublayer on both sides: `x -> x + after_mixer(mixer(norm1(x)))`, then
+`x -> x + after_ffn(ffn(norm2(x)))`.  A sublayer's output cannot be added by its last projection
+here (it is normed first), so the sublayer hands over its output as a weighted sum of float32
+rows (`branches`) and the norm after it sums, norms and adds in one launch.  A layer of this
+arrangement may have no feed-forward; it then has no norms around one either.
 """
 from __future__ import annotations
 
@@ -14,6 +20,8 @@ class PreNormBlock(Block):
     def __init__(self, norm1, mixer, norm2, ffn, **more_norms):
         if norm1 is None or norm2 is None or more_norms:
             raise ValueError("block 'pre_norm' has exactly two norms: one before the mixer, one before the feed-forward")
+        if ffn is None:
+            raise ValueError("block 'pre_norm' has a feed-forward")
         super().__init__(norm1, mixer, norm2, ffn)
 
 
@@ -27,4 +35,28 @@ class PreNormBlock(Block):
         return self.ffn.forward(ctx, h, x)
 
 
+class SandwichBlock(Block):
+    def __init__(self, norm1, mixer, norm2, ffn, after_mixer=None, after_ffn=None, **more_norms):
+        if norm1 is None or after_mixer is None or more_norms:
+            raise ValueError("block 'sandwich' has a norm before the mixer and one named 'after_mixer'")
+        if (ffn is None) != (norm2 is None) or (ffn is None) != (after_ffn is None):
+            raise ValueError("block 'sandwich' has a feed-forward with a norm before it and one named 'after_ffn', "
+                             "or none of the three")
+        extra = {"after_mixer": after_mixer} if ffn is None else {"after_mixer": after_mixer, "after_ffn": after_ffn}
+        super().__init__(norm1, mixer, norm2, ffn, **extra)
+
+    def forward(self, ctx, x, app):
+        announce = getattr(ctx.ops, "announce_weights", None)
+        if announce is not None:
+            announce(self.mixer.stream_weights() + (self.ffn.stream_weights() if self.ffn is not None else [])
+                     + list(getattr(ctx, "next_weights", ())))
+        h = self.norm1.forward(ctx, x, ctx.dtype)
+        x = self.more_norms["after_mixer"].add_normed(ctx, x, self.mixer.branches(ctx, h, app))
+        if self.ffn is None:
+            return x
+        h = self.norm2.forward(ctx, x, ctx.dtype)
+        return self.more_norms["after_ffn"].add_normed(ctx, x, self.ffn.branches(ctx, h))
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)

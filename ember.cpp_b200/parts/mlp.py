@@ -4,6 +4,11 @@ ember.cpp's GPT-2 block: `u = h Wup^T + b; u = gelu(u); f = u Wdown^T + b; x = x
 (graph_ir.cpp:743-746, 754-756) with GELU in its tanh form
 `0.5 v (1 + tanh(sqrt(2/pi) (v + 0.044715 v^3)))` or its erf form `0.5 v (1 + erf(v / sqrt 2))`
 (graph_ir.cpp:2471-2481; graph_ir_cuda.cu:230-242).
+
+Gated feed-forward: two projections of the input side by side, `y = act(g) * u`, then the down
+projection.  `silu`: act(g) = g * sigmoid(g), the usual gated layer.  `clamped_sigmoid`: g is first
+capped from above at `limit` and u held within +-`limit`, then y = g * sigmoid(alpha * g) * (u + shift).
+The two matrices are laid one under the other at load, so a step makes one product for both.
 """
 from __future__ import annotations
 
@@ -61,4 +66,52 @@ class DenseFeedForward(FeedForward):
         return ctx.ops.linear(u, self.w_down, self.b_down, residual=residual)
 
 
+GATES = ("silu", "clamped_sigmoid")
+
+
+class GatedFeedForward(FeedForward):
+
+    def __init__(self, prefix: str, width: int, inner: int, activation: str = "silu", limit: float = 0.0,
+                 alpha: float = 1.0, shift: float = 0.0, gate: str = "gate", up: str = "up", down: str = "down",
+                 suffix: str = ".weight", init_std: float = 0.02, down_init_std: float = 0.02):
+        super().__init__(prefix)
+        if activation not in GATES:
+            raise ValueError(f"feed-forward {prefix!r}: activation {activation!r} is not one of {GATES}")
+        if activation == "clamped_sigmoid" and not limit > 0:
+            raise ValueError(f"feed-forward {prefix!r}: limit = {limit} must be positive")
+        self.width, self.inner, self.activation = int(width), int(inner), activation
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.gate_name, self.up_name, self.down_name = (prefix + n + suffix for n in (gate, up, down))
+        self.init_std, self.down_init_std = init_std, down_init_std
+        self.w_gate_up = self.w_down = None
+
+    def weight_specs(self):
+        return [WeightSpec(self.gate_name, (self.inner, self.width), std=self.init_std),
+                WeightSpec(self.up_name, (self.inner, self.width), std=self.init_std),
+                WeightSpec(self.down_name, (self.width, self.inner), std=self.down_init_std)]
+
+    def load(self, get, runtime):
+        import torch
+        if runtime.dtype == torch.bfloat16 and (self.inner % 8 or self.width % 8):
+            raise ValueError(f"feed-forward {self.prefix!r}: the bfloat16 kernels take widths that are multiples of 8 "
+                             f"(here width {self.width}, inner {self.inner}); the float32 path takes this model")
+        self.w_gate_up = torch.cat([runtime.matrix(get(self.gate_name)), runtime.matrix(get(self.up_name))]).contiguous()
+        self.w_down = runtime.matrix(get(self.down_name))
+
+    def stream_weights(self):
+        return [self.w_gate_up, self.w_down]
+
+    def _inner(self, ctx, h):
+        gu = ctx.ops.linear(h, self.w_gate_up, None, out_dtype=ctx.dtype)          # [T, gate | up]
+        return ctx.ops.gated_act(gu, self.activation, self.limit, self.alpha, self.shift)
+
+    def forward(self, ctx, h, residual):
+        return ctx.ops.linear(self._inner(ctx, h), self.w_down, None, residual=residual)
+
+    def branches(self, ctx, h):
+        import torch
+        return [(ctx.ops.linear(self._inner(ctx, h), self.w_down, None, out_dtype=torch.float32), 1.0)]
+
+
 register_part("ffn", "dense", DenseFeedForward)
+register_part("ffn", "gated", GatedFeedForward)

@@ -25,11 +25,12 @@ class DecoderModel:
         for layer in spec.layers:
             norm = lambda part: None if part is None else build_part("norm", part)  # noqa: E731
             self.blocks.append(build_block(layer.block, norm(layer.norm1), build_part("mixer", layer.mixer), norm(layer.norm2),
-                                           build_part("ffn", layer.ffn), {name: norm(part) for name, part in layer.more_norms}))
+                                           None if layer.ffn is None else build_part("ffn", layer.ffn), {name: norm(part) for name, part in layer.more_norms}))
         self.final_norm = build_part("norm", spec.final_norm)
         self.table = None
         self.head = None
         self.head_bias = None
+        self.reads_tokens = any(getattr(p, "needs_tokens", False) for p in self.all_parts())
 
     # ------------------------------------------------------------------ tensors
     def all_parts(self):
@@ -83,6 +84,10 @@ class DecoderModel:
         logits [wanted rows, vocab] (None if no row is wanted)."""
         plan, ops = ctx.plan, ctx.ops
         ids = getattr(plan, "device_ids", None)   # sampled ids on the device that this step's tokens are taken from
+        if ids is not None and self.reads_tokens:
+            # a part looks its tokens up in a table of its own: the ids are put into the description first
+            ops.take_tokens(plan.tokens, plan.token_src, ids, self.spec.vocab_size)
+            ids = None
         if ids is not None:
             x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table(),
                           token_src=plan.token_src, ids=ids)

@@ -4,6 +4,9 @@ LayerNorm with bias as ember.cpp computes it: mean and biased variance in two pa
 `(x - mean) * 1/sqrt(var + eps) * w + b` (graph_ir.cpp:2421-2439; the CUDA kernel
 graph_ir_cuda.cu:47-65 accumulates both sums in double).  Here the statistics are in float32 on
 the residual stream, which is float32 in every mode.
+
+RMS norm: `x / sqrt(mean(x^2) + eps) * (offset + w)`, the statistics in float32 too.  `offset` is
+0 for a gain stored as it is used and 1 for a gain stored as its distance from one.  No bias.
 """
 from __future__ import annotations
 
@@ -31,4 +34,29 @@ class LayerNorm(Norm):
         return ctx.ops.layernorm(x, self.w, self.b, self.eps, out_dtype)
 
 
+class RMSNorm(Norm):
+
+    def __init__(self, prefix: str, width: int, eps: float, weight: str = "weight", offset: float = 0.0,
+                 init_std: float = 0.02):
+        super().__init__(prefix)
+        self.width, self.eps, self.offset = int(width), float(eps), float(offset)
+        self.weight_name, self.init_std = prefix + weight, init_std
+        self.w = None
+
+    def weight_specs(self):
+        # random-weights mode: the gain as used is 1 + N(0, std)
+        return [WeightSpec(self.weight_name, (self.width,), mean=1.0 - self.offset, std=self.init_std)]
+
+    def load(self, get, runtime):
+        self.w = runtime.vector(get(self.weight_name))
+
+    def forward(self, ctx, x, out_dtype):
+        return ctx.ops.rmsnorm(x, self.w, self.eps, out_dtype, offset=self.offset)
+
+    def add_normed(self, ctx, x, branches):
+        """One launch: the weighted sum of the branches, its norm, and the sum with the stream."""
+        return ctx.ops.add_normed(x, branches, self.w, self.eps, offset=self.offset)
+
+
 register_part("norm", "layernorm", LayerNorm)
+register_part("norm", "rmsnorm", RMSNorm)

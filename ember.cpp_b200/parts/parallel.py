@@ -1,0 +1,85 @@
+"""Mixers side by side: several mixers read the same normed input and their outputs are added,
+each with a fixed factor.
+
+The members are ordinary mixers, given as PartSpecs and built through the registry, so any two
+(an attention and a recurrence, two attentions with different windows) can be paired.  At most
+one of them may want a cache (a schedule entry has one view of it); their per-sequence states are
+kept apart under the member's name.
+"""
+from __future__ import annotations
+
+import dataclasses
+
+from .base import Mixer, build_part, register_part
+from .spec import PartSpec
+
+
+class ParallelMixers(Mixer):
+
+    def __init__(self, prefix: str, width: int, members):
+        """members: (name, PartSpec or its (kind, prefix, params), factor) per mixer; a member's tensor
+        prefix is given whole (it does not inherit this part's)."""
+        super().__init__(prefix)
+        self.width = int(width)
+        self.members = []
+        for name, spec, factor in members:
+            if not isinstance(spec, PartSpec):
+                spec = PartSpec(*spec)
+            self.members.append((str(name), build_part("mixer", spec), float(factor)))
+        if not self.members:
+            raise ValueError(f"parallel mixers {prefix!r}: no members")
+        if sum(1 for _, m, _ in self.members if m.cache_need() is not None) > 1:
+            raise ValueError(f"parallel mixers {prefix!r}: more than one member wants a cache")
+        self.graph_safe = all(m.graph_safe for _, m, _ in self.members)
+
+    def weight_specs(self):
+        return [w for _, m, _ in self.members for w in m.weight_specs()]
+
+    def load(self, get, runtime):
+        for _, m, _ in self.members:
+            m.load(get, runtime)
+
+    def stream_weights(self):
+        return [w for _, m, _ in self.members for w in m.stream_weights()]
+
+    def cache_need(self):
+        for _, m, _ in self.members:
+            if m.cache_need() is not None:
+                return m.cache_need()
+        return None
+
+    def state_need(self):
+        need = {}
+        for name, m, _ in self.members:
+            s = m.state_need()
+            if s is None:
+                continue
+            for key, one in (s.items() if isinstance(s, dict) else [("", s)]):
+                need[f"{name}.{key}"] = one
+        return need or None
+
+    def _handle(self, app, name, member):
+        """The schedule entry as one member sees it: its own state (under its own names), the cache if it wants one."""
+        s = member.state_need()
+        if s is None:
+            state = None
+        elif isinstance(s, dict):
+            state = {key: app.state[f"{name}.{key}"] for key in s}
+        else:
+            state = app.state[f"{name}."]
+        return dataclasses.replace(app, state=state)
+
+    def branches(self, ctx, h, app):
+        out = []
+        for name, m, factor in self.members:
+            out += [(rows, f * factor) for rows, f in m.branches(ctx, h, self._handle(app, name, m))]
+        return out
+
+    def forward(self, ctx, h, residual, app):
+        x = residual
+        for rows, f in self.branches(ctx, h, app):
+            x = x + f * rows
+        return x
+
+
+register_part("mixer", "parallel", ParallelMixers)

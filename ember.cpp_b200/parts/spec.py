@@ -28,12 +28,13 @@ class LayerSpec:
     """One layer's parts.  `block` names the arrangement (how norms, mixer, feed-forward and
     the residual stream are wired).  An arrangement with one shared norm leaves `norm2` None; one
     with more norms than two (norms after the mixer and after the feed-forward as well) names the
-    others in `more_norms`, and its block receives them as keyword arguments of those names."""
+    others in `more_norms`, and its block receives them as keyword arguments of those names.  A
+    layer without a feed-forward leaves `ffn` None (its arrangement must allow that)."""
     block: str
     norm1: PartSpec | None
     mixer: PartSpec
     norm2: PartSpec | None
-    ffn: PartSpec
+    ffn: PartSpec | None
     more_norms: tuple[tuple[str, PartSpec], ...] = ()
 
 

@@ -32,7 +32,11 @@ def random_tensor(spec: WeightSpec, seed: int, dtype: torch.dtype, device="cpu")
     """Drawn on `device`; the values of a seed are those of that device's generator (a model
     folder is always written from the CPU's)."""
     if spec.integer:
-        raise ValueError(f"random weights: no rule for the integer table {spec.name!r}")
+        # rows of distinct values below `below`: the first entries of a random order, row by row
+        if spec.below <= 0 or len(spec.shape) != 2 or spec.shape[1] > spec.below:
+            raise ValueError(f"random weights: no rule for the integer table {spec.name!r}")
+        noise = torch.rand((spec.shape[0], spec.below), generator=_generator(seed, spec.name, device), device=device)
+        return noise.argsort(dim=1)[:, :spec.shape[1]].to(torch.int32).contiguous()
     t = torch.empty(spec.shape, dtype=torch.float32, device=device)
     t.normal_(spec.mean, spec.std, generator=_generator(seed, spec.name, device))
     return t.to(dtype)

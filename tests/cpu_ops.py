@@ -49,10 +49,11 @@ class CpuOps:
                 for t in list(group.k) + list(group.v):
                     t[page, :, row:, :] = 0
 
-    def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim):
+    def kv_store(self, qkv, cache, plan, n_heads, kv_heads, head_dim, value_dim=None):
         g = cache.group_index
         q_w = n_heads * head_dim
         kv_w = kv_heads * head_dim
+        vd = head_dim if value_dim is None else value_dim
         for t in range(plan.T):
             s = int(plan.token_seq[t])
             if int(plan.seq_slot[s]) < 0:
@@ -61,13 +62,15 @@ class CpuOps:
             page = int(plan.pages[g][s, p // PAGE])
             assert page >= 0, "a position is written whose page is not held"
             cache.k[page, :, p % PAGE, :] = qkv[t, q_w:q_w + kv_w].view(kv_heads, head_dim).to(cache.k.dtype)
-            cache.v[page, :, p % PAGE, :] = qkv[t, q_w + kv_w:].view(kv_heads, head_dim).to(cache.v.dtype)
+            cache.v[page, :, p % PAGE, :] = qkv[t, q_w + kv_w:q_w + kv_w + kv_heads * vd].view(kv_heads, vd).to(cache.v.dtype)
 
-    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False):
+    def attention(self, qkv, cache, plan, n_heads, kv_heads, head_dim, scale, window, out_dtype, store=False,
+                  keep_first=0, value_dim=None):
         if store:
-            self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim)
+            self.kv_store(qkv, cache, plan, n_heads, kv_heads, head_dim, value_dim)
         g = cache.group_index
-        out = torch.zeros(plan.T, n_heads * head_dim)
+        vd = head_dim if value_dim is None else value_dim
+        out = torch.zeros(plan.T, n_heads * vd)
         rep = n_heads // kv_heads
         for t in range(plan.T):
             s = int(plan.token_seq[t])
@@ -76,6 +79,8 @@ class CpuOps:
             p = int(plan.positions[t])
             lo = max(0, p - window + 1) if window > 0 else 0
             pos = torch.arange(lo, p + 1)
+            if window > 0 and keep_first > 0 and lo > 0:
+                pos = torch.cat([torch.arange(0, min(keep_first, lo)), pos])
             pages = plan.pages[g][s, pos // PAGE].long()
             assert (pages >= 0).all(), "a position is read whose page is not held"
             k = cache.k[pages, :, pos % PAGE, :].float()      # [keys, kv_heads, hd]
@@ -84,8 +89,102 @@ class CpuOps:
             for h in range(n_heads):
                 sc = (k[:, h // rep, :] @ q[h]) * scale
                 pr = torch.softmax(sc, 0)
-                out[t, h * head_dim:(h + 1) * head_dim] = pr @ v[:, h // rep, :]
+                out[t, h * vd:(h + 1) * vd] = pr @ v[:, h // rep, :]
         return out.to(out_dtype)
+
+    # ------------------------------------------------------------------ RMS norm, gates
+    def rmsnorm(self, x, w, eps, out_dtype, offset=0.0):
+        x = x.float()
+        return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * (offset + w)).to(out_dtype)
+
+    def add_normed(self, x, branches, w, eps, offset=0.0):
+        total = None
+        for rows, factor in branches:
+            term = rows.float() * factor
+            total = term if total is None else total + term
+        x += self.rmsnorm(total, w, eps, torch.float32, offset)
+        return x
+
+    def gated_act(self, gu, activation, limit=0.0, alpha=1.0, shift=0.0):
+        n = gu.shape[1] // 2
+        g, u = gu[:, :n].float(), gu[:, n:].float()
+        if activation == "silu":
+            y = g * torch.sigmoid(g) * u
+        else:
+            g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+            y = g * torch.sigmoid(alpha * g) * (u + shift)
+        return y.to(gu.dtype)
+
+    # ------------------------------------------------------------------ Mamba-2
+    @staticmethod
+    def _sequences(plan):
+        slots, starts, cu = plan.seq_slot.tolist(), plan.seq_start.tolist(), plan.cu_new.tolist()
+        return [(slots[i], starts[i], cu[i], cu[i + 1]) for i in range(plan.n)]
+
+    def conv_silu(self, proj, col0, channels, conv_w, conv_b, conv_state, plan):
+        taps = conv_w.shape[1]
+        out = torch.zeros(proj.shape[0], channels)
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            u = proj[t0:t1, col0:col0 + channels].float()
+            if taps > 1:
+                before = conv_state[slot].clone() if start > 0 else torch.zeros(taps - 1, channels)
+                u = torch.cat([before, u])
+                conv_state[slot] = u[-(taps - 1):]
+            acc = conv_b.clone().expand(t1 - t0, channels).clone()
+            for j in range(taps):
+                acc += conv_w[:, j] * u[j:j + t1 - t0]
+            out[t0:t1] = acc * torch.sigmoid(acc)
+        return out.to(proj.dtype)
+
+    def ssd_scan(self, xbc, proj, dt_col, dt_bias, a_log, skip, state, plan, heads, vdim, groups, n_state):
+        inner, gn = heads * vdim, groups * n_state
+        y = torch.zeros(xbc.shape[0], inner)
+        per = heads // groups
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            S = state[slot].clone() if start > 0 else torch.zeros(heads, vdim, n_state)
+            for t in range(t0, t1):
+                x = xbc[t, :inner].float().view(heads, vdim)
+                B = xbc[t, inner:inner + gn].float().view(groups, n_state).repeat_interleave(per, 0)
+                C = xbc[t, inner + gn:inner + 2 * gn].float().view(groups, n_state).repeat_interleave(per, 0)
+                dt = torch.nn.functional.softplus(proj[t, dt_col:dt_col + heads].float() + dt_bias)
+                a = torch.exp(-torch.exp(a_log) * dt)
+                S = a[:, None, None] * S + (dt[:, None] * x)[:, :, None] * B[:, None, :]
+                y[t] = ((S * C[:, None, :]).sum(-1) + skip[:, None] * x).reshape(-1)
+            state[slot] = S
+        return y
+
+    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype):
+        n = y.shape[1]
+        z = proj[:, z_col:z_col + n].float()
+        g = (y * z * torch.sigmoid(z)).view(y.shape[0], parts, n // parts)
+        g = g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)
+        return (g.reshape(y.shape[0], n) * w).to(out_dtype)
+
+    # ------------------------------------------------------------------ experts by table
+    def moe_route(self, tokens, T, table, experts, top):
+        return table[tokens[:T].long()].long()            # [T, top]: the expert of every (token, choice) pair
+
+    def moe_gate_up(self, h, w_gate_up, routing, out_dtype):
+        T, top = routing.shape
+        n = w_gate_up.shape[1] // 2
+        out = torch.zeros(T * top, n)
+        for t in range(T):
+            for k in range(top):
+                gu = w_gate_up[routing[t, k]].float() @ h[t].float()
+                out[t * top + k] = gu[:n] * torch.sigmoid(gu[:n]) * gu[n:]
+        return out.to(out_dtype)
+
+    def moe_down(self, inner, w_down, routing):
+        T, top = routing.shape
+        out = torch.zeros(T, top, w_down.shape[1])
+        for t in range(T):
+            for k in range(top):
+                out[t, k] = w_down[routing[t, k]].float() @ inner[t * top + k].float()
+        return out
 
     def scale_cap(self, x, scale=1.0, cap=None):
         x.mul_(scale)
