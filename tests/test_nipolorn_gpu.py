@@ -1,0 +1,347 @@
+"""Nipolorn on the GPU: every mechanism's kernels against the plain implementation, then whole
+models through the engine (prompts, token-by-token decoding, portions, unequal batches, slots and
+pages used again, long decoding, graph replay) and greedy generation through the session."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import ember_cpp_b200 as E
+from ember_cpp_b200.cache.sequence_cache import SequenceCache
+from ember_cpp_b200.engine.plan import StepPlan, build_step
+from ember_cpp_b200.parts import CacheNeed
+
+import nipolorn_util as U
+import plain_nipolorn as P
+from conftest import run_batch
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+OP_TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from ember_cpp_b200.csrc.ops import CudaOps
+    return CudaOps()
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    return {name: U.write_model(str(tmp_path_factory.mktemp(name)), U.config(name), U.SEEDS[name]) for name in U.CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def plains(folders):
+    return {name: P.PlainNipolorn(folder) for name, folder in folders.items()}
+
+
+def rnd(seed, *shape, scale=1.0):
+    return torch.randn(*shape, generator=torch.Generator().manual_seed(seed)) * scale
+
+
+def f64(t):
+    return t.detach().double().cpu().numpy()
+
+
+def close(got, want, tol):
+    got, want = f64(got) if torch.is_tensor(got) else got, np.asarray(want, dtype=np.float64)
+    assert got.shape == want.shape
+    assert np.abs(got - want).max() <= tol * max(np.abs(want).max(), 1e-9), np.abs(got - want).max() / np.abs(want).max()
+
+
+def plan_of(seqs):
+    """seqs: (slot, positions held, new tokens); a step's description without a cache."""
+    host = build_step([(s, [0] * n, []) for s, _, n in seqs], {s: a for s, a, _ in seqs}, [], 1)
+    return StepPlan(host, torch.from_numpy(host.packed).cuda())
+
+
+# ------------------------------------------------------------------------------ norms and gates
+@pytest.mark.parametrize("out", ["float32", "bfloat16"])
+@pytest.mark.parametrize("rows, d, offset", [(1, 8, 1.0), (33, 200, 1.0), (5, 1030, 0.0)])
+def test_rmsnorm(ops, out, rows, d, offset):
+    x, w = rnd(1, rows, d, scale=3.0), rnd(2, d, scale=0.2)
+    want = P.rms_unit(f64(x), 1e-5) * (offset + f64(w))
+    close(ops.rmsnorm(x.cuda(), w.cuda(), 1e-5, DT[out], offset), want, OP_TOL[out])
+
+
+def test_add_normed_sums_norms_and_adds_in_one_launch(ops):
+    rows, d = 21, 136
+    x, w = rnd(1, rows, d), rnd(2, d, scale=0.1)
+    wide = rnd(3, rows, 3, d).cuda()
+    branches = [(wide[:, k, :], 1 / 3) for k in range(3)] + [(rnd(4, rows, d).cuda(), 0.7)]
+    total = sum(f64(t) * f for t, f in branches)
+    before = ops.launches
+    got = ops.add_normed(x.clone().cuda(), branches, w.cuda(), 1e-6, 1.0)
+    assert ops.launches == before + 1
+    close(got, f64(x) + P.offset_rms_norm(total, f64(w), 1e-6), 2e-6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_gates(ops, dtype):
+    gu = rnd(5, 17, 2 * 40, scale=2.5).to(DT[dtype])
+    g, u = f64(gu[:, :40]), f64(gu[:, 40:])
+    close(ops.gated_act(gu.cuda(), "silu"), P.silu(g) * u, OP_TOL[dtype])
+    for limit in (0.5, 3.0):
+        gc, uc = np.minimum(g, limit), np.clip(u, -limit, limit)
+        close(ops.gated_act(gu.cuda(), "clamped_sigmoid", limit, 1.702, 1.0), gc * P.sigmoid(1.702 * gc) * (uc + 1.0), OP_TOL[dtype])
+
+
+# ------------------------------------------------------------------------------ Mamba-2
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, vdim, groups, N, taps, parts", [(6, 20, 2, 24, 4, 3), (2, 16, 2, 8, 2, 1), (3, 48, 1, 130, 3, 2),
+                                                               (4, 8, 4, 5, 1, 4)])
+def test_convolution_recurrence_and_gated_norm_over_steps(ops, dtype, heads, vdim, groups, N, taps, parts):
+    """Three sequences fed in unequal steps (prompts, portions, one token each, a padding sequence in between)
+    with the state rows carried by slot, against the plain functions on the whole sequences.  The state rows start
+    as NaN: a sequence that begins must not read them."""
+    dt = DT[dtype]
+    inner, gn = heads * vdim, groups * N
+    ch, width = inner + 2 * gn, 2 * inner + 2 * gn + heads
+    stride = -(-width // 8) * 8
+    cw, cb = rnd(1, ch, taps, scale=0.4), rnd(2, ch, scale=0.1)
+    dtb, alog, skip, nw = rnd(3, heads, scale=0.5) - 1, rnd(4, heads, scale=0.5) - 0.5, rnd(5, heads) + 1, rnd(6, inner, scale=0.1) + 1
+    lengths = {3: 47, 1: 44, 4: 9}
+    data = {s: rnd(10 + s, n, stride).to(dt) for s, n in lengths.items()}
+    conv_state = torch.full((5, max(taps - 1, 1), ch), float("nan")).cuda() if taps > 1 else None
+    ssm_state = torch.full((5, heads, vdim, N), float("nan")).cuda()
+    got = {s: [] for s in lengths}
+    at = {s: 0 for s in lengths}
+    for step in ([(3, 2), (1, 41), (4, 1)], [(3, 37), (1, 1), (4, 2)], [(1, 1), (-1, 1), (3, 1), (4, 1)], [(4, 5), (3, 7)], [(1, 1)]):
+        seqs = [(s, at.get(s, 0), n) for s, n in step]
+        plan = plan_of(seqs)
+        proj = torch.cat([data[s][at[s]:at[s] + n] if s >= 0 else torch.zeros(n, stride, dtype=dt) for s, _, n in seqs]).cuda()
+        xbc = ops.conv_silu(proj, inner, ch, cw.cuda(), cb.cuda(), conv_state, plan)
+        y = ops.ssd_scan(xbc, proj, 2 * inner + 2 * gn, dtb.cuda(), alog.cuda(), skip.cuda(), ssm_state, plan, heads, vdim, groups, N)
+        out = ops.gated_group_norm(y, proj, 0, nw.cuda(), parts, 1e-6, dt)
+        row = 0
+        for s, _, n in seqs:
+            if s >= 0:
+                got[s].append((xbc[row:row + n], y[row:row + n], out[row:row + n]))
+                at[s] += n
+            row += n
+    for s, n in lengths.items():
+        proj = f64(data[s])
+        xbc = P.causal_conv_silu(proj[:, inner:inner + ch], f64(cw), f64(cb))
+        close(torch.cat([g[0] for g in got[s]]), xbc, OP_TOL[dtype])
+        xbc_used = f64(torch.cat([g[0] for g in got[s]]))                  # the recurrence reads the rounded rows
+        dts = P.softplus(proj[:, 2 * inner + 2 * gn:width] + f64(dtb))
+        y = P.ssd_recurrence(xbc_used[:, :inner], xbc_used[:, inner:inner + gn], xbc_used[:, inner + gn:], dts, f64(alog), f64(skip),
+                             heads, vdim, groups, N)
+        close(torch.cat([g[1] for g in got[s]]), y, 3e-5)
+        y_used = f64(torch.cat([g[1] for g in got[s]]))
+        close(torch.cat([g[2] for g in got[s]]), P.gated_group_norm(y_used, proj[:, :inner], f64(nw), parts, 1e-6), OP_TOL[dtype])
+
+
+def test_the_recurrence_remembers_a_token_from_far_back(ops):
+    """Decay close to one: a single large input 600 tokens back is what the output is made of."""
+    heads, vdim, N, T = 1, 16, 8, 640
+    xbc = torch.zeros(T, vdim + 2 * N)
+    xbc[:, vdim:] = 1.0                       # B = C = ones
+    xbc[20, :vdim] = 50.0
+    proj = torch.zeros(T, 8)
+    proj[:, 0] = -4.0                         # dt = softplus(-4)
+    state = torch.zeros(1, heads, vdim, N).cuda()
+    y = ops.ssd_scan(xbc.cuda(), proj.cuda(), 0, torch.zeros(1).cuda(), torch.tensor([-3.0]).cuda(), torch.zeros(1).cuda(), state,
+                     plan_of([(0, 0, T)]), heads, vdim, 1, N)
+    dt = P.softplus(np.full((T, 1), -4.0))
+    want = P.ssd_recurrence(f64(xbc[:, :vdim]), f64(xbc[:, vdim:vdim + N]), f64(xbc[:, vdim + N:]), dt, np.array([-3.0]), np.zeros(1), 1, vdim, 1, N)
+    assert want[-1].min() > 1.0
+    close(y, want, 2e-5)
+
+
+# ------------------------------------------------------------------------------ attention with kept first tokens
+def attention_steps(ops, dtype, heads, kv, hd, vd, window, keep, steps, qkv_of, scale):
+    """Feeds sequences step by step through the paged cache (pages taken in a scrambled order, NaN in every page
+    before) and returns the outputs per sequence."""
+    need = CacheNeed("window", kv, hd, window, keep, 0 if vd == hd else vd)
+    cache = SequenceCache([(need, None)], [None], 4096, None, DT[dtype], "cuda")
+    cache.groups[0].pages._free = np.random.default_rng(0).permutation(cache.n_pages).tolist()
+    view = cache.views[0]
+    view.k.fill_(float("nan"))
+    view.v.fill_(float("nan"))
+    n_seq = len(steps[0])
+    slots = [cache.open() for _ in range(n_seq)]
+    outs = [[] for _ in range(n_seq)]
+    at = [0] * n_seq
+    for news in steps:
+        live = [(i, n) for i, n in enumerate(news) if n > 0]
+        entries = [(slots[i], n) for i, n in live]
+        tails = cache.reserve(entries)
+        host = build_step([(s, [0] * n, []) for s, n in entries], cache.lengths, [cache.groups[0].table], cache.max_blocks, tails=tails)
+        plan = StepPlan(host, torch.from_numpy(host.packed).cuda())
+        if plan.has_tails:
+            ops.clear_tails(cache.groups[0], plan.tails[0])
+        qkv = torch.cat([qkv_of(i)[at[i]:at[i] + n] for i, n in live]).to(DT[dtype]).cuda().contiguous()
+        out = ops.attention(qkv, view, plan, heads, kv, hd, scale, window, DT[dtype], store=True, keep_first=keep, value_dim=vd)
+        cache.commit(entries)
+        row = 0
+        for i, n in live:
+            outs[i].append(out[row:row + n])
+            at[i] += n
+            row += n
+    cache.check()
+    return [torch.cat(o) for o in outs]
+
+
+def plain_attention_rows(qkv, heads, kv, hd, vd, window, keep, scale):
+    qkv = f64(qkv)
+    T, per = qkv.shape[0], heads // kv
+    q = qkv[:, :heads * hd].reshape(T, heads, hd)
+    k = qkv[:, heads * hd:(heads + kv) * hd].reshape(T, kv, hd)
+    v = qkv[:, (heads + kv) * hd:].reshape(T, kv, vd)
+    out = np.zeros((T, heads, vd))
+    for i in range(T):
+        js = [j for j in range(i + 1) if P.visible(i, j, window, keep)]
+        for a in range(heads):
+            s = np.array([q[i, a] @ k[j, a // per] for j in js]) * scale
+            p = np.exp(s - s.max())
+            out[i, a] = (p / p.sum()) @ v[js, a // per]
+    return out.reshape(T, heads * vd)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, kv, hd, vd, window, keep", [(4, 2, 48, 48, 70, 5), (6, 3, 24, 40, 33, 66), (2, 1, 64, 64, 130, 0),
+                                                            (4, 4, 32, 32, 64, 64), (2, 2, 16, 16, 1, 1)])
+def test_attention_with_window_and_kept_first_tokens(ops, dtype, heads, kv, hd, vd, window, keep):
+    """Prompts of unequal length, portions on top of a cache, one token each; windows shorter and longer than a
+    page, kept tokens within one page and across two; values wider than keys."""
+    lengths = (290, 7, 140)
+    width = (heads + kv) * hd + kv * vd
+    data = [rnd(20 + i, n, width).to(DT[dtype]) for i, n in enumerate(lengths)]
+    steps = [[200, 3, 70], [1, 1, 1], [1, 1, 1], [80, 2, 60], [1, 0, 1], [7, 0, 7]]
+    scale = 0.9 / math.sqrt(hd)
+    got = attention_steps(ops, dtype, heads, kv, hd, vd, window, keep, steps, lambda i: data[i], scale)
+    for g, d in zip(got, data):
+        close(g, plain_attention_rows(d, heads, kv, hd, vd, window, keep, scale), OP_TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("prompt", [True, False])
+def test_one_marked_key_is_seen_exactly_where_the_rule_says(ops, dtype, prompt):
+    """One key matches the queries strongly and carries a value of 100: the output of a query is about 100 if
+    the rule lets it see that key and near 0 if not.  The marked key is placed at the last kept position, the
+    first position that is not kept, and far back; queries just inside and just outside the window, in a
+    prompt's rows and in rows decoded one by one."""
+    heads, kv, hd, window, keep = 2, 1, 32, 96, 6
+    T = 330
+    for marked in (0, keep - 1, keep, 100, 191):
+        def qkv_of(_):
+            qkv = rnd(marked, T, (heads + 2 * kv) * hd, scale=0.1)
+            qkv[:, :heads * hd] += 6.0 * torch.ones(hd).repeat(heads)               # every query points along ones
+            qkv[marked, heads * hd:(heads + kv) * hd] = 6.0                         # the marked key too
+            qkv[:, (heads + kv) * hd:] = 0.0
+            qkv[marked, (heads + kv) * hd:] = 100.0
+            return qkv
+        steps = [[T]] if prompt else [[marked + 2]] + [[1]] * (T - marked - 2)
+        got = f64(attention_steps(ops, dtype, heads, kv, hd, hd, window, keep, steps, qkv_of, 1.0)[0])[:, 0]
+        for i in (marked, marked + 1, marked + window - 1, marked + window, marked + window + 1, T - 1):
+            if i < T:
+                seen = P.visible(i, marked, window, keep)
+                assert (got[i] > 99.0) if seen else (abs(got[i]) < 1e-2), (marked, i, seen, got[i])
+
+
+# ------------------------------------------------------------------------------ experts by table
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("experts, top, width, ff, T", [(5, 2, 72, 40, 3), (5, 2, 72, 40, 150), (3, 3, 64, 136, 70), (9, 1, 200, 8, 129)])
+def test_experts_by_table(ops, dtype, experts, top, width, ff, T):
+    dt, vocab = DT[dtype], 31
+    g = torch.Generator().manual_seed(7)
+    table = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(vocab)]).int()
+    wgu, wd = rnd(1, experts, 2 * ff, width, scale=0.15).to(dt), rnd(2, experts, width, ff, scale=0.15).to(dt)
+    toks, h = torch.randint(0, vocab, (T,), generator=g).int(), rnd(3, T, width).to(dt)
+    plain_experts = [(f64(wgu[e, :ff]), f64(wgu[e, ff:]), f64(wd[e])) for e in range(experts)]
+    want = P.table_experts(f64(h), toks.tolist(), table.numpy(), plain_experts, None)
+    routing = ops.moe_route(toks.cuda(), T, table.cuda(), experts, top)
+    assert routing[1].tolist() == np.concatenate([[0], np.cumsum(np.bincount(table[toks.long()].flatten().numpy(), minlength=experts))]).tolist()
+    assert sorted(routing[2].tolist()) == list(range(T * top))
+    for tiled in ((False, True) if dtype == "bfloat16" else (False,)):
+        inner = ops.moe_gate_up(h.cuda(), wgu.cuda(), routing, dt, tiled=tiled)
+        y = ops.moe_down(inner, wd.cuda(), routing, tiled=tiled)
+        close(y.sum(1) / top, want, 3e-5 if dtype == "float32" else 2e-2)
+
+
+# ------------------------------------------------------------------------------ whole models through the engine
+@pytest.fixture(scope="module")
+def engines(folders):
+    return {(name, dtype): E.Engine.from_folder(folders[name], dtype=dtype, max_tokens=2048)
+            for name in folders for dtype in ("float32", "bfloat16")}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["nip_a", "nip_b"])
+def test_prompts_decoding_portions_and_batches_equal_the_plain_model(engines, plains, name, dtype):
+    eng, m = engines[(name, dtype)], plains[name]
+    vocab = m.cfg["vocab"]
+    seqs = [U.ids(10 + i, vocab, n) for i, n in enumerate((200, 1, 40, 97, 2))]
+    refs = [P.forward(m, s) for s in seqs]
+    for prompts in ([len(s) for s in seqs], [150, 1, 1, 30, 1]):
+        got, _ = run_batch(eng, seqs, prompts)
+        assert max(U.row_error(g, r) for g, r in zip(got, refs)) < U.TOL[dtype]
+    each_alone = [run_batch(eng, [s], [min(len(s), 33)])[0][0] for s in seqs]          # alone: no neighbour changes a row
+    assert max(U.row_error(g, r) for g, r in zip(each_alone, refs)) < U.TOL[dtype]
+    slot, at, rows = eng.open(), 0, []
+    for n in (2, 5, 64, 3, 2, 30, 94):                                                 # portions of one sequence
+        rows.append(eng.step([(slot, seqs[0][at:at + n], list(range(n)))]).cpu().numpy())
+        at += n
+    eng.close(slot)
+    assert U.row_error(np.concatenate(rows), refs[0]) < U.TOL[dtype]
+    eng.ops.check()
+    eng.cache.check()
+    assert eng.cache.slots.held == 0 and all(g.pages.held == 0 for g in eng.cache.groups)
+
+
+def test_in_32_bit_a_row_does_not_depend_on_the_batch_or_the_cut(engines):
+    """Every sum of the 32-bit path is made in an order that the row's own sequence fixes."""
+    eng = engines[("nip_a", "float32")]
+    seqs = [U.ids(70 + i, 300, n) for i, n in enumerate((90, 31, 64))]
+    together, _ = run_batch(eng, seqs, [60, 31, 1])
+    for i, s in enumerate(seqs):
+        alone, _ = run_batch(eng, [s], [len(s)])
+        assert np.abs(alone[0] - together[i]).max() < 2e-5 * np.abs(alone[0]).max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_past_the_window_with_slots_used_again(folders, plains, dtype):
+    """A small cache: sequences decoded far past the window hold few pages, and the next batch gets the
+    slots, state rows and pages that the batch before it left (filled with NaN in between)."""
+    eng, m = E.Engine.from_folder(folders["nip_a"], dtype=dtype, max_tokens=384), plains["nip_a"]
+    for round_ in range(2):
+        seqs = [U.ids(200 * round_ + i, 300, n) for i, n in enumerate((330, 90))]
+        got, slots = run_batch(eng, seqs, [3, 70])
+        assert sorted(slots) == [0, 1]
+        assert max(U.row_error(g, P.forward(m, s)) for g, s in zip(got, seqs)) < U.TOL[dtype]
+        for g in eng.cache.groups:
+            for t in g.k + g.v:
+                t.fill_(float("nan"))
+        for state in eng.cache.states:
+            for t in state.values():
+                t.fill_(float("nan"))
+    assert max(g.pages.size for g in eng.cache.groups) == 6
+
+
+def test_graph_replay_equals_launch_by_launch(folders):
+    seqs = [U.ids(300 + i, 300, n) for i, n in enumerate((40, 75, 9))]
+    outs = []
+    for graphs in (True, False):
+        eng = E.Engine.from_folder(folders["nip_a"], dtype="float32", max_tokens=1024, cuda_graphs=graphs)
+        assert eng.cuda_graphs == graphs
+        outs.append(run_batch(eng, seqs, [20, 60, 1])[0])
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_session(folders, plains, dtype):
+    for name in ("nip_a", "nip_b"):
+        m = plains[name]
+        session = E.Session(folders[name], None, max_batch_size=3, dtype=dtype, max_tokens=2048)
+        prompts = [U.ids(50 + i, m.cfg["vocab"], n) for i, n in enumerate((5, 23, 1, 9))]
+        got = session.generate_batch(prompts, steps=8, temperature=0.0)
+        want = [P.generate(m, p, 8) for p in prompts]
+        if dtype == "float32":
+            assert got == want
+        else:       # a near tie may fall the other way in bfloat16: the first tokens agree, and most of the rest
+            assert [g[0] for g in got] == [w[0] for w in want]
+            assert sum(a == b for g, w in zip(got, want) for a, b in zip(g, w)) >= 24
