@@ -215,6 +215,113 @@ def linear_mode(args) -> int:
     return 0
 
 
+DESIGN_SIZES = {
+    # width, layers, attention heads / kv heads / head size, window, kept first, Mamba-2 heads / vdim / groups / state,
+    # dense inner, experts / top / expert inner / shared inner, vocabulary
+    "small": dict(width=1024, layers=4, heads=16, kv_heads=4, dim=64, window=512, keep=4, m_heads=32, m_vdim=64, m_groups=1,
+                  m_state=64, ff=4096, experts=16, top=2, expert_ff=512, shared_ff=1024, vocab=32000),
+    "medium": dict(width=2048, layers=4, heads=16, kv_heads=4, dim=128, window=1024, keep=4, m_heads=64, m_vdim=64, m_groups=2,
+                   m_state=128, ff=8192, experts=32, top=2, expert_ff=1024, shared_ff=2048, vocab=32000),
+}
+
+
+def design_configs(size: str):
+    """(Nipolorn configuration, GPT-2 configuration of equal width, layers, heads and dense inner size)."""
+    z = DESIGN_SIZES[size]
+    left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
+            "mask": {"size": z["window"], "keep_first": z["keep"]}}
+    right = {"heads": z["m_heads"], "vdim": z["m_vdim"], "groups": z["m_groups"], "state": z["m_state"], "conv": 4, "norm_groups": z["m_groups"]}
+    mixer = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.9}
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared_ff"]}}
+    layers = [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0} if i == 0 else moe}
+              for i in range(z["layers"])]
+    nip = {"architecture": "Nipolorn", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6}, "layers": layers}
+    gpt = {"architectures": ["GPT2LMHeadModel"], "vocab_size": z["vocab"], "n_positions": 4096, "n_embd": z["width"], "n_layer": z["layers"],
+           "n_head": z["width"] // z["dim"], "n_inner": z["ff"], "tie_word_embeddings": False}
+    return nip, gpt
+
+
+def design_mode(args) -> int:
+    """Prefill and decode throughput of a Nipolorn model beside a GPT-2 of equal width, layers, head size and dense
+    inner size, both with random bfloat16 weights: a prompt of `--prompt-len` tokens (default 2,048) in one step,
+    and one-token steps of `--batch` sequences at that context; CUDA-event times, the median of five prompts and the
+    mean of `--steps` replayed steps after `--warmup`.  Then the same two steps launch by launch with an event
+    around every launch: the time of each kernel entry point, which is what the kernels' rooflines are read from.
+    One JSON line a model."""
+    import numpy as np
+    import torch
+
+    import ember_cpp_b200 as E
+    from ember_cpp_b200.config import config_from_dict, get_architecture
+    from ember_cpp_b200.engine import Engine
+    from ember_cpp_b200.parts import DecoderModel
+    from ember_cpp_b200.weights import random_tensors
+
+    prompt_len = args.prompt_len if args.prompt_len != PROMPT_LEN else 2048
+    B, K, W = args.batch, args.steps or 64, max(3, args.warmup)
+    rng = np.random.default_rng(0)
+    pk = peaks()
+    for cfgd in design_configs(args.design_size):
+        config = config_from_dict(cfgd)
+        spec = get_architecture(config.architecture).build_spec(config)
+        tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
+        n_params = sum(t.numel() for t in tensors.values() if t.dtype.is_floating_point)
+        record = {"model": config.architecture, "size": args.design_size, "parameters": n_params, "prompt_len": prompt_len, "batch": B,
+                  "dtype": "bf16", "data": "synthetic", "peaks": pk}
+        for timing in (False, True):
+            opt = E.RuntimeOptions(dtype="bfloat16", max_tokens=(B + 1) * (prompt_len + K + W + 128), op_timing=timing)
+            eng = Engine.from_spec(spec, tensors, options=opt)
+            vocab = spec.vocab_size
+            prompt = rng.integers(0, vocab, prompt_len).tolist()
+            times = []
+            for _ in range(2 if timing else 7):                    # whole prompts, one sequence a step
+                slot = eng.open()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                if timing:
+                    eng.ops.op_times()
+                a.record()
+                eng.step([(slot, prompt, [prompt_len - 1])])
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b))
+                eng.close(slot)
+            if timing:
+                record["prefill_kernels_ms"] = {k: [n, round(ms, 4)] for k, (n, ms) in sorted(eng.ops.op_times().items())}
+            else:
+                record["prefill_ms"] = round(statistics.median(times[2:]), 3)
+                record["prefill_tok_s"] = round(prompt_len / statistics.median(times[2:]) * 1e3)
+            slots = [eng.open() for _ in range(B)]
+            eng.step([(s, rng.integers(0, vocab, prompt_len).tolist(), []) for s in slots])
+            if not timing:
+                eng.capture_decode(B)
+            step = lambda: eng.step([(s, [int(t)], [0]) for s, t in zip(slots, rng.integers(0, vocab, B))], borrow=True)  # noqa: E731
+            for _ in range(W):
+                step()
+            torch.cuda.synchronize()
+            if timing:
+                eng.ops.op_times()
+                step()
+                record["decode_kernels_ms"] = {k: [n, round(ms, 4)] for k, (n, ms) in sorted(eng.ops.op_times().items())}
+            else:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(K):
+                    step()
+                b.record()
+                torch.cuda.synchronize()
+                record["decode_ms_per_step"] = round(a.elapsed_time(b) / K, 4)
+                record["decode_tok_s"] = round(B * K / a.elapsed_time(b) * 1e3)
+            eng.ops.check()
+            for s in slots:
+                eng.close(s)
+            del eng
+            torch.cuda.empty_cache()
+        print(json.dumps(record), flush=True)
+        del tensors
+        torch.cuda.empty_cache()
+    return 0
+
+
 def umma_issue_mode() -> int:
     """Cycles per tcgen05.mma by shape and by the way it is issued (see csrc/umma_probe.cu)."""
     from ember_cpp_b200.csrc.ops import CudaOps
@@ -252,12 +359,17 @@ def main() -> int:
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
     ap.add_argument("--residual", action="store_true", help="with --linear: add a float32 residual (the output is float32 then)")
+    ap.add_argument("--design", default=None, choices=["nipolorn"],
+                    help="instead of the benchmark: prefill and decode throughput of this design beside a GPT-2 of equal size")
+    ap.add_argument("--design-size", default="medium", choices=sorted(DESIGN_SIZES), help="with --design: the layers' sizes")
     ap.add_argument("--umma-issue", action="store_true", help="print what a tcgen05.mma costs to issue, by shape and way of issuing")
     args = ap.parse_args()
     if args.umma_issue:
         return umma_issue_mode()
     if args.linear:
         return linear_mode(args)
+    if args.design:
+        return design_mode(args)
     if args.impl == "reference":
         return reference_arm(args)
     if args.gpus != 1:

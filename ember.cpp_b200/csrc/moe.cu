@@ -8,8 +8,8 @@
 //   gate_up   inner[q, :] = silu(Wg_e a_t) * (Wu_e a_t)     (W_e = [gate | up] stacked, [2 * inner, width])
 //   down      y[q, :]     = Wd_e inner[q, :]                (float32)
 // Few pairs (a decode step): a warp per output value streams the expert's rows once, which is all the
-// traffic there is.  Many pairs (a prompt): tiles of 64 pairs x 64 outputs of one expert on mma.sync
-// m16n8k16 with cp.async double buffering.  float32 takes the streaming form at every size: one
+// traffic there is.  Many pairs (a prompt): tiles of one expert's pairs and outputs on mma.sync
+// m16n8k16 with cp.async double buffering (tiles of 128 pairs x 64 outputs).  float32 takes the streaming form at every size: one
 // fixed order of additions per output value, no reduced-precision matrix mode.
 #include "common.cuh"
 
@@ -105,8 +105,9 @@ moe_down_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, const i
 }
 
 // ---------------------------------------------------------------------------- tiled form (bfloat16)
-constexpr int kTile = 64;   // pairs a tile, and outputs a tile
-constexpr int kStep = 32;   // of the summed dimension per trip
+constexpr int kTileM = 128;  // pairs a tile
+constexpr int kTileN = 64;   // outputs a tile
+constexpr int kStep = 64;    // of the summed dimension per trip
 constexpr int kLd = kStep + 8;
 
 __device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
@@ -128,25 +129,31 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+template <bool GATED>
+constexpr int tile_smem() {
+  return (2 * kTileM * kLd + 2 * (GATED ? 2 : 1) * kTileN * kLd) * (int)sizeof(__nv_bfloat16);
+}
+
 // GATED: W_e = [gate | up] of n_out rows each, the result silu(gate) * up in bfloat16 and the input rows are
 // the tokens' (pair / top); else W_e has n_out rows, the result is float32 and the input rows are the pairs'.
 // grid (tiles of pairs: an upper bound, ceil(n_out / 64)); a block finds its expert and its tile of that
-// expert's pairs from the offsets, and leaves if there is none.
+// expert's pairs from the offsets, and leaves if there is none.  Four warps, each 32 pairs x 64 outputs.
 template <bool GATED>
 __global__ void __launch_bounds__(128)
 moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ w, const int* __restrict__ offsets,
                 const int* __restrict__ sorted, void* __restrict__ out, int experts, int top, int K, int n_out) {
   constexpr int NW = GATED ? 2 : 1;
-  __shared__ __align__(16) __nv_bfloat16 sA[2][kTile * kLd];
-  __shared__ __align__(16) __nv_bfloat16 sW[2][NW][kTile * kLd];
-  __shared__ int s_rows[kTile];  // the input row of each of the tile's pairs, -1 past the expert's last
-  __shared__ int s_pair[kTile];
-  __shared__ int s_expert;
+  extern __shared__ __align__(16) unsigned char tile_raw[];
+  __nv_bfloat16* sA = reinterpret_cast<__nv_bfloat16*>(tile_raw);  // [2][kTileM * kLd]
+  __nv_bfloat16* sW = sA + 2 * kTileM * kLd;                       // [2][NW][kTileN * kLd]
+  __shared__ int s_rows[kTileM];  // the input row of each of the tile's pairs, -1 past the expert's last
+  __shared__ int s_pair[kTileM];
+  __shared__ int s_expert, s_tile;
 
   if (threadIdx.x == 0) {
     int tile = blockIdx.x, found = -1;
     for (int e = 0; e < experts; ++e) {
-      const int tiles = (offsets[e + 1] - offsets[e] + kTile - 1) / kTile;
+      const int tiles = (offsets[e + 1] - offsets[e] + kTileM - 1) / kTileM;
       if (tile < tiles) {
         found = e;
         break;
@@ -154,47 +161,50 @@ moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __rest
       tile -= tiles;
     }
     s_expert = found;
-    s_pair[0] = tile;  // (handed to the others below)
+    s_tile = tile;
   }
   __syncthreads();
   const int e = s_expert;
   if (e < 0) return;
-  const int tile = s_pair[0];
-  __syncthreads();
-  const int first = offsets[e] + tile * kTile, count = min(kTile, offsets[e + 1] - first);
-  if ((int)threadIdx.x < kTile) {
+  const int first = offsets[e] + s_tile * kTileM, count = min(kTileM, offsets[e + 1] - first);
+  {
     const int q = (int)threadIdx.x < count ? sorted[first + threadIdx.x] : -1;
     s_pair[threadIdx.x] = q;
     s_rows[threadIdx.x] = q < 0 ? -1 : (GATED ? q / top : q);
   }
   __syncthreads();
 
-  const int n0 = blockIdx.y * kTile;
+  const int n0 = blockIdx.y * kTileN;
   const __nv_bfloat16* we = w + (size_t)e * NW * n_out * K;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   auto load = [&](int buf, int k0) {
     constexpr int CPR = kStep / 8;  // 16-byte pieces a row
-    for (int id = threadIdx.x; id < kTile * CPR; id += 128) {
+    for (int id = threadIdx.x; id < kTileM * CPR; id += 128) {
       const int r = id / CPR, c = id % CPR;
-      const bool in_k = k0 + c * 8 < K;
       const int src = s_rows[r];
-      const bool ok_a = src >= 0 && in_k;
-      cp_async_16(&sA[buf][r * kLd + c * 8], a + (ok_a ? (size_t)src * K + k0 + c * 8 : 0), ok_a);
-      const bool ok_w = n0 + r < n_out && in_k;
+      const bool ok = src >= 0 && k0 + c * 8 < K;
+      cp_async_16(sA + (size_t)buf * kTileM * kLd + r * kLd + c * 8, a + (ok ? (size_t)src * K + k0 + c * 8 : 0), ok);
+    }
+    for (int id = threadIdx.x; id < kTileN * CPR; id += 128) {
+      const int r = id / CPR, c = id % CPR;
+      const bool ok = n0 + r < n_out && k0 + c * 8 < K;
 #pragma unroll
       for (int m = 0; m < NW; ++m)
-        cp_async_16(&sW[buf][m][r * kLd + c * 8], we + (ok_w ? ((size_t)m * n_out + n0 + r) * K + k0 + c * 8 : 0), ok_w);
+        cp_async_16(sW + ((size_t)buf * NW + m) * kTileN * kLd + r * kLd + c * 8,
+                    we + (ok ? ((size_t)m * n_out + n0 + r) * K + k0 + c * 8 : 0), ok);
     }
   };
 
-  float acc[NW][8][4];
+  float acc[NW][2][8][4];
 #pragma unroll
   for (int m = 0; m < NW; ++m)
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int f = 0; f < 2; ++f)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) acc[m][i][j] = 0.f;
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[m][f][i][j] = 0.f;
 
   const int trips = (K + kStep - 1) / kStep;
   load(0, 0);
@@ -209,18 +219,25 @@ moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __rest
       cp_async_wait<0>();
     }
     __syncthreads();
+    const __nv_bfloat16* tA = sA + (size_t)buf * kTileM * kLd;
 #pragma unroll
     for (int ks = 0; ks < kStep / 16; ++ks) {
-      unsigned af[4];
-      ldmatrix_x4(af, &sA[buf][(warp * 16 + (lane & 15)) * kLd + ks * 16 + (lane >> 4) * 8]);
+      unsigned af[2][4];
+#pragma unroll
+      for (int f = 0; f < 2; ++f)
+        ldmatrix_x4(af[f], tA + (warp * 32 + f * 16 + (lane & 15)) * kLd + ks * 16 + (lane >> 4) * 8);
 #pragma unroll
       for (int m = 0; m < NW; ++m) {
+        const __nv_bfloat16* tW = sW + ((size_t)buf * NW + m) * kTileN * kLd;
 #pragma unroll
         for (int np = 0; np < 4; ++np) {
           unsigned b[4];
-          ldmatrix_x4(b, &sW[buf][m][(np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + ks * 16 + ((lane >> 3) & 1) * 8]);
-          mma_bf16(acc[m][2 * np], af, b[0], b[1]);
-          mma_bf16(acc[m][2 * np + 1], af, b[2], b[3]);
+          ldmatrix_x4(b, tW + (np * 16 + (lane & 7) + (lane >> 4) * 8) * kLd + ks * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+          for (int f = 0; f < 2; ++f) {
+            mma_bf16(acc[m][f][2 * np], af[f], b[0], b[1]);
+            mma_bf16(acc[m][f][2 * np + 1], af[f], b[2], b[3]);
+          }
         }
       }
     }
@@ -229,24 +246,50 @@ moe_tile_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __rest
 
   const int g = lane >> 2, c2 = (lane & 3) * 2;
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    const int q = s_pair[warp * 16 + g + r * 8];
-    if (q < 0) continue;
+  for (int f = 0; f < 2; ++f) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int r = 0; r < 2; ++r) {
+      const int q = s_pair[warp * 32 + f * 16 + g + r * 8];
+      if (q < 0) continue;
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int n = n0 + i * 8 + c2 + j;
+      for (int i = 0; i < 8; ++i) {
+        const int n = n0 + i * 8 + c2;  // this thread's two outputs: n and n + 1 (n_out is even where rows are 16-byte pieces)
         if (n >= n_out) continue;
         if constexpr (GATED) {
-          const float gv = acc[0][i][2 * r + j], uv = acc[1][i][2 * r + j];
-          static_cast<__nv_bfloat16*>(out)[(size_t)q * n_out + n] = __float2bfloat16_rn(gv / (1.0f + expf(-gv)) * uv);
+          const float g0 = acc[0][f][i][2 * r], g1 = acc[0][f][i][2 * r + 1];
+          const float y0 = g0 / (1.0f + expf(-g0)) * acc[1][f][i][2 * r], y1 = g1 / (1.0f + expf(-g1)) * acc[1][f][i][2 * r + 1];
+          __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(out) + (size_t)q * n_out + n;
+          if (n + 1 < n_out)
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(y0, y1);
+          else
+            *dst = __float2bfloat16_rn(y0);
         } else {
-          static_cast<float*>(out)[(size_t)q * n_out + n] = acc[0][i][2 * r + j];
+          float* dst = static_cast<float*>(out) + (size_t)q * n_out + n;
+          if (n + 1 < n_out)
+            *reinterpret_cast<float2*>(dst) = make_float2(acc[0][f][i][2 * r], acc[0][f][i][2 * r + 1]);
+          else
+            *dst = acc[0][f][i][2 * r];
         }
       }
     }
   }
+}
+
+template <bool GATED>
+int launch_tiles(const void* a, const void* w, const int* offsets, const int* sorted, void* out, long long pairs, int experts,
+                 int top, int K, int n_out, cudaStream_t stream, const char* name) {
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(moe_tile_kernel<GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, tile_smem<GATED>());
+    if (e != cudaSuccess) return ember_fail("%s: %s", name, cudaGetErrorString(e));
+    configured = true;
+  }
+  const dim3 grid((unsigned)((pairs + kTileM - 1) / kTileM + experts), (n_out + kTileN - 1) / kTileN);
+  EMBER_CHECK(grid.y <= 65535, "%s: %d outputs exceed one launch", name, n_out);
+  moe_tile_kernel<GATED><<<grid, 128, tile_smem<GATED>(), stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, offsets,
+                                                                    sorted, out, experts, top, K, n_out);
+  EMBER_LAUNCH_OK(name);
+  return 0;
 }
 
 }  // namespace
@@ -271,13 +314,9 @@ EMBER_API int ember_moe_gate_up(const void* a, const void* w, const int* pair_ex
   EMBER_CHECK(T > 0 && top > 0 && experts > 0 && width > 0 && inner > 0, "moe_gate_up: bad sizes");
   const long long pairs = (long long)T * top;
   if (tiled) {
-    EMBER_CHECK(dtype == EMBER_BF16 && width % 8 == 0, "moe_gate_up: tiles take bfloat16 rows that are multiples of 8");
-    const dim3 grid((unsigned)((pairs + kTile - 1) / kTile + experts), (inner + kTile - 1) / kTile);
-    EMBER_CHECK(grid.y <= 65535, "moe_gate_up: %d outputs exceed one launch", inner);
-    moe_tile_kernel<true><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, offsets, sorted, out,
-                                                    experts, top, width, inner);
-    EMBER_LAUNCH_OK("moe_gate_up");
-    return 0;
+    EMBER_CHECK(dtype == EMBER_BF16 && width % 8 == 0 && inner % 2 == 0,
+                "moe_gate_up: tiles take bfloat16 rows that are multiples of 8 and an even number of outputs");
+    return launch_tiles<true>(a, w, offsets, sorted, out, pairs, experts, top, width, inner, stream, "moe_gate_up");
   }
   const dim3 grid((unsigned)pairs, (inner + kStreamWarps * kStreamOutputs - 1) / (kStreamWarps * kStreamOutputs));
   EMBER_CHECK(grid.y <= 65535, "moe_gate_up: %d outputs exceed one launch", inner);
@@ -300,13 +339,9 @@ EMBER_API int ember_moe_down(const void* a, const void* w, const int* pair_exper
   EMBER_CHECK(T > 0 && top > 0 && experts > 0 && width > 0 && inner > 0, "moe_down: bad sizes");
   const long long pairs = (long long)T * top;
   if (tiled) {
-    EMBER_CHECK(dtype == EMBER_BF16 && inner % 8 == 0, "moe_down: tiles take bfloat16 rows that are multiples of 8");
-    const dim3 grid((unsigned)((pairs + kTile - 1) / kTile + experts), (width + kTile - 1) / kTile);
-    EMBER_CHECK(grid.y <= 65535, "moe_down: %d outputs exceed one launch", width);
-    moe_tile_kernel<false><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, offsets, sorted, out,
-                                                     experts, top, inner, width);
-    EMBER_LAUNCH_OK("moe_down");
-    return 0;
+    EMBER_CHECK(dtype == EMBER_BF16 && inner % 8 == 0 && width % 2 == 0,
+                "moe_down: tiles take bfloat16 rows that are multiples of 8 and an even number of outputs");
+    return launch_tiles<false>(a, w, offsets, sorted, out, pairs, experts, top, inner, width, stream, "moe_down");
   }
   const dim3 grid((unsigned)pairs, (width + kStreamWarps * kStreamOutputs - 1) / (kStreamWarps * kStreamOutputs));
   EMBER_CHECK(grid.y <= 65535, "moe_down: %d outputs exceed one launch", width);

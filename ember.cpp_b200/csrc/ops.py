@@ -66,10 +66,12 @@ _SIGNATURES = {
                                 _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_attention_prefill_kept": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
                                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
+    "ember_attention_decode_kept": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_void],
     "ember_conv_silu": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
-                        _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void],
+                        _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_ssd_scan": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
-                       _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+                       _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
     "ember_moe_route": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
     "ember_moe_gate_up": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_void],
@@ -128,6 +130,12 @@ def load_library() -> ctypes.CDLL:
     lib.ember_set_option.restype = _c_int
     lib.ember_attention_decode_partials.argtypes = [_c_int] * 5
     lib.ember_attention_decode_partials.restype = _c_size
+    lib.ember_ssd_scan_piece.argtypes = []
+    lib.ember_ssd_scan_piece.restype = _c_int
+    lib.ember_ssd_scan_scratch.argtypes = [_c_int] * 5
+    lib.ember_ssd_scan_scratch.restype = _c_size
+    lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
+    lib.ember_attention_decode_kept_scratch.restype = _c_size
     for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
                  "ember_attention_decode_mma_status"):
         getattr(lib, name).argtypes = []
@@ -597,6 +605,18 @@ class CudaOps:
             self._call("ember_kv_store_v", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), plan.positions.data_ptr(),
                        plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.T,
                        n_heads, kv_heads, hd, vd, _code(qkv.dtype))
+        if qkv.dtype == torch.bfloat16 and plan.all_single and plan.T == plan.n:
+            # one token each: the visible keys in chunks of 128, a block a chunk and key/value head, then the merge
+            max_keys = min(keep_first + window, plan.max_end) if window > 0 else plan.max_end
+            scratch = torch.empty(self.lib.ember_attention_decode_kept_scratch(plan.T, n_heads, vd, max_keys),
+                                  dtype=torch.float32, device=qkv.device)
+            rc = self._call("ember_attention_decode_kept", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
+                            out.data_ptr(), scratch.data_ptr(), plan.positions.data_ptr(), plan.seq_slot.data_ptr(),
+                            pages.data_ptr(), plan.max_blocks, plan.T, n_heads, kv_heads, hd, vd, float(scale), int(window),
+                            keep_first, int(max_keys), allow=(2,))
+            if rc == 0:
+                self.launches += 1      # (the merge)
+                return out
         if qkv.dtype == torch.bfloat16 and vd == hd and scale > 0 and not plan.all_single:
             rc = self._call("ember_attention_prefill_kept", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
@@ -669,7 +689,7 @@ class CudaOps:
         self._call("ember_conv_silu", proj.data_ptr(), proj.stride(0), int(col0), int(channels), int(taps), conv_w.data_ptr(),
                    conv_b.data_ptr(), self._ptr(conv_state), out.data_ptr(), plan.token_seq.data_ptr(),
                    plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.T, plan.n,
-                   1 if plan.all_single else 0, _code(proj.dtype))
+                   max(int(plan.max_new), 1), 1 if plan.all_single else 0, _code(proj.dtype))
         return out
 
     def ssd_scan(self, xbc, proj, dt_col, dt_bias, a_log, skip, state, plan, heads, vdim, groups, n_state):
@@ -682,9 +702,17 @@ class CudaOps:
             raise KernelError("ssd_scan: the state is float32 [slots, heads, vdim, states]")
         self._dense(xbc, "x | B | C")
         y = torch.empty((plan.T, inner), dtype=torch.float32, device=xbc.device)
+        # a step with a long sequence scans every sequence in pieces side by side (see ssm.cu)
+        piece = self.lib.ember_ssd_scan_piece()
+        pieces = -(-plan.max_new // piece) if plan.max_new >= 2 * piece else 1
+        scratch = None
+        if pieces > 1:
+            scratch = torch.empty(self.lib.ember_ssd_scan_scratch(plan.n, pieces, heads, vdim, n_state), dtype=torch.float32,
+                                  device=xbc.device)
         self._call("ember_ssd_scan", xbc.data_ptr(), proj.data_ptr(), proj.stride(0), int(dt_col), dt_bias.data_ptr(),
                    a_log.data_ptr(), skip.data_ptr(), state.data_ptr(), y.data_ptr(), plan.seq_slot.data_ptr(),
-                   plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.n, heads, vdim, groups, n_state, _code(xbc.dtype))
+                   plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.n, heads, vdim, groups, n_state, pieces,
+                   self._ptr(scratch), _code(xbc.dtype))
         return y
 
     def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype):

@@ -75,4 +75,6 @@ def row_error(got, ref) -> float:
     return float((np.sqrt((d * d).mean(-1)) / np.sqrt((r * r).mean(-1))).max())
 
 
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# of a row's spread (see row_error).  bfloat16: these models' weights are scaled up so that every mechanism shows in
+# the logits, which also lets the roundings of activations through: the engine is within this of the exact rows
+TOL = {"float32": 2e-5, "bfloat16": 8e-2}
