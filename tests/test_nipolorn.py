@@ -183,3 +183,17 @@ def test_greedy_generation_through_the_session(folders, plains):
         prompts = [U.ids(50 + i, m.cfg["vocab"], n) for i, n in enumerate((5, 23, 1, 9))]
         out = session.generate_batch(prompts, steps=6, temperature=0.0)
         assert out == [P.generate(m, p, 6) for p in prompts]
+
+
+def test_the_command_line_writes_a_random_model_of_this_design(tmp_path, capsys):
+    from ember_cpp_b200 import cli
+    cfg_file = tmp_path / "cfg.json"
+    cfg_file.write_text(json.dumps(U.config("nip_b")))
+    out = tmp_path / "model"
+    assert cli.main([str(out), "-", "1", "random-weights", "--config", str(cfg_file), "--seed", "5"]) == 0
+    cfg = E.load_config(str(out))
+    assert isinstance(cfg, NipolornConfig) and cfg.width == 96
+    eng = cpu_engine(str(out), max_tokens=128)
+    slot = eng.open()
+    logits = eng.step([(slot, U.ids(1, 200, 9), [8])])
+    assert tuple(logits.shape) == (1, 200) and bool(torch.isfinite(logits).all())
