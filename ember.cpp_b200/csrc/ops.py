@@ -72,6 +72,8 @@ _SIGNATURES = {
                         _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_ssd_scan": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
                        _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_int, _c_void],
+    "ember_ssd_pieces": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void,
+                         _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
     "ember_moe_route": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void],
     "ember_moe_gate_up": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_void],
@@ -132,6 +134,8 @@ def load_library() -> ctypes.CDLL:
     lib.ember_attention_decode_partials.restype = _c_size
     lib.ember_ssd_scan_piece.argtypes = []
     lib.ember_ssd_scan_piece.restype = _c_int
+    lib.ember_ssd_pieces_len.argtypes = []
+    lib.ember_ssd_pieces_len.restype = _c_int
     lib.ember_ssd_scan_scratch.argtypes = [_c_int] * 5
     lib.ember_ssd_scan_scratch.restype = _c_size
     lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
@@ -692,7 +696,10 @@ class CudaOps:
                    max(int(plan.max_new), 1), 1 if plan.all_single else 0, _code(proj.dtype))
         return out
 
-    def ssd_scan(self, xbc, proj, dt_col, dt_bias, a_log, skip, state, plan, heads, vdim, groups, n_state):
+    SSD_PIECES_FROM = 128   # new tokens of a step's longest sequence from which the recurrence runs as matrix products
+
+    def ssd_scan(self, xbc, proj, dt_col, dt_bias, a_log, skip, state, plan, heads, vdim, groups, n_state,
+                 tensor_cores=None):
         """The recurrence of parts/ssm.py over the step's sequences: xbc [T, x | B | C], the raw step sizes in
         `heads` columns from dt_col of `proj`, state float32 [slots, heads, vdim, n_state] (advanced); float32 y."""
         inner = heads * vdim
@@ -702,6 +709,21 @@ class CudaOps:
             raise KernelError("ssd_scan: the state is float32 [slots, heads, vdim, states]")
         self._dense(xbc, "x | B | C")
         y = torch.empty((plan.T, inner), dtype=torch.float32, device=xbc.device)
+        # prompts in bfloat16: pieces of 64 tokens as matrix products on the tensor cores, where the sizes have
+        # an instantiation (tensor_cores: None lets the step's shape decide, False takes the scalar scan)
+        if tensor_cores is None:
+            tensor_cores = plan.max_new >= self.SSD_PIECES_FROM
+        if tensor_cores and xbc.dtype == torch.bfloat16:
+            pieces = max(1, -(-plan.max_new // self.lib.ember_ssd_pieces_len()))
+            scratch = torch.empty(self.lib.ember_ssd_scan_scratch(plan.n, max(pieces, 2), heads, vdim, n_state),
+                                  dtype=torch.float32, device=xbc.device)
+            rc = self._call("ember_ssd_pieces", xbc.data_ptr(), proj.data_ptr(), proj.stride(0), int(dt_col),
+                            dt_bias.data_ptr(), a_log.data_ptr(), skip.data_ptr(), state.data_ptr(), y.data_ptr(),
+                            plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), plan.n, heads, vdim,
+                            groups, n_state, pieces, scratch.data_ptr(), allow=(2,))
+            if rc == 0:
+                self.launches += 2
+                return y
         # a step with a long sequence scans every sequence in pieces side by side (see ssm.cu)
         piece = self.lib.ember_ssd_scan_piece()
         pieces = -(-plan.max_new // piece) if plan.max_new >= 2 * piece else 1

@@ -316,12 +316,12 @@ ssd_scan_kernel(const T* __restrict__ xbc, const T* __restrict__ dt_in, long lon
 __global__ void ssd_carry_kernel(float* __restrict__ state, float* __restrict__ piece_state,
                                  const float* __restrict__ piece_decay, const int* __restrict__ seq_slot,
                                  const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads,
-                                 int per_head, int pieces) {
+                                 int per_head, int pieces, int piece_len) {
   const int s = blockIdx.z, h = blockIdx.y;
   const int e = blockIdx.x * blockDim.x + threadIdx.x;
   const int slot = seq_slot[s];
   if (e >= per_head || slot < 0) return;
-  const int n_pieces = min(pieces, (cu_new[s + 1] - cu_new[s] + kSplit - 1) / kSplit);
+  const int n_pieces = min(pieces, (cu_new[s + 1] - cu_new[s] + piece_len - 1) / piece_len);
   float* st = state + ((size_t)slot * heads + h) * per_head + e;
   float S = seq_start[s] > 0 ? *st : 0.f;
   for (int i = 0; i < n_pieces; ++i) {
@@ -372,13 +372,343 @@ int launch_scan(const void* xbc, const void* dt_in, long long dt_stride, int dt_
     EMBER_SCAN(kLocal);
     const int per_head = vdim * N;
     ssd_carry_kernel<<<dim3((per_head + 255) / 256, heads, n_seqs), 256, 0, stream>>>(
-        state, piece_state, piece_decay, seq_slot, seq_start, cu_new, heads, per_head, pieces);
+        state, piece_state, piece_decay, seq_slot, seq_start, cu_new, heads, per_head, pieces, kSplit);
     EMBER_SCAN(kFinal);
   }
 #undef EMBER_SCAN
 #undef EMBER_SCAN_MODE
 #undef EMBER_SCAN_ARGS
   EMBER_LAUNCH_OK("ssd_scan");
+  return 0;
+}
+
+
+// ---------------------------------------------------------------------------- recurrence on the tensor cores
+// For prompts in bfloat16 the recurrence of a piece of 64 tokens is three matrix products (the form that gives
+// Mamba-2 its name).  With la_t the running sum of log decays inside the piece (la_t = A * sum_{s<=t} dt_s <= 0):
+//   end state from zeros   E[p][n] = sum_s x_s[p] * (exp(la_end - la_s) dt_s B_s[n])
+//   inside the piece       y_t    += sum_{s<=t} (C_t . B_s) exp(la_t - la_s) dt_s x_s
+//   from the piece's start y_t    += exp(la_t) * (C_t . S_start)
+// x, B and C are bfloat16 values, so their products are exact in float32 accumulators (mma.sync m16n8k16).  The
+// factors that are float32 (the decays times B, the decayed scores, the state) enter as two bfloat16 terms, the
+// value rounded and what the rounding left (hi + lo: about 16 bits of mantissa, two products instead of one), so
+// the float32 quantities of the recurrence keep far more than bfloat16's precision; sums and the state itself are
+// float32.  Every exponent is of a difference <= 0.  The pieces' starting states come from the same carry kernel
+// as the scalar scan's.  Instantiated for states of 64 and 128 rows and 64 value channels; other sizes, float32
+// and short steps take the scalar scan.
+constexpr int kL = 64;
+
+__device__ __forceinline__ void ldsm_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_16816(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// v as a rounded bfloat16 and the bfloat16 of what the rounding left
+__device__ __forceinline__ void split_bf16(float v, __nv_bfloat16& hi, __nv_bfloat16& lo) {
+  hi = __float2bfloat16_rn(v);
+  lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+__device__ __forceinline__ unsigned pack2(__nv_bfloat16 a, __nv_bfloat16 b) {
+  return (unsigned)__bfloat16_as_ushort(a) | ((unsigned)__bfloat16_as_ushort(b) << 16);
+}
+
+// Step sizes and running log decays of the piece's tokens (zero steps past its end), by the first warp.
+__device__ __forceinline__ void piece_decays(const __nv_bfloat16* __restrict__ dt_in, long long dt_stride, int dt_col, int h,
+                                             float bias, float A, int tc, int cnt, float* s_la, float* s_dt) {
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float d[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int tt = lane + 32 * k;
+      d[k] = tt < cnt ? softplus_f(__bfloat162float(dt_in[(size_t)(tc + tt) * dt_stride + dt_col + h]) + bias) : 0.f;
+    }
+    float run[2] = {d[0], d[1]};
+#pragma unroll
+    for (int k = 0; k < 2; ++k)
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float v = __shfl_up_sync(0xffffffffu, run[k], off);
+        if (lane >= off) run[k] += v;
+      }
+    run[1] += __shfl_sync(0xffffffffu, run[0], 31);
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      s_dt[lane + 32 * k] = d[k];
+      s_la[lane + 32 * k] = A * run[k];
+    }
+  }
+}
+
+// grid (1, heads, sequences * pieces): the end state of a piece from zeros, transposed [p][n], and its decay.
+template <int N, int P>
+__global__ void __launch_bounds__(128)
+ssd_piece_state_kernel(const __nv_bfloat16* __restrict__ xbc, const __nv_bfloat16* __restrict__ dt_in, long long dt_stride,
+                       int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                       const int* __restrict__ seq_slot, const int* __restrict__ cu_new, int heads, int groups, int pieces,
+                       float* __restrict__ piece_state, float* __restrict__ piece_decay) {
+  constexpr int LDN = N + 8, LDL = kL + 8;
+  extern __shared__ __align__(16) unsigned char raw[];
+  __nv_bfloat16* sXt = reinterpret_cast<__nv_bfloat16*>(raw);  // [P][LDL]: x transposed
+  __nv_bfloat16* sBh = sXt + P * LDL;                           // [kL][LDN]: decayed B, rounded
+  __nv_bfloat16* sBl = sBh + kL * LDN;                          //            and what the rounding left
+  __shared__ float s_la[kL], s_dt[kL];
+  const int s = blockIdx.z / pieces, piece = blockIdx.z % pieces, h = blockIdx.y;
+  if (seq_slot[s] < 0) return;
+  const int tc = cu_new[s] + piece * kL, cnt = min(kL, cu_new[s + 1] - tc);
+  if (cnt <= 0) return;
+  const int inner = heads * P, gn = groups * N, g = h / (heads / groups);
+  const size_t stride = (size_t)inner + 2 * gn;
+  piece_decays(dt_in, dt_stride, dt_col, h, dt_bias[h], -expf(a_log[h]), tc, cnt, s_la, s_dt);
+  __syncthreads();
+  const float la_end = s_la[kL - 1];
+  for (int e = threadIdx.x; e < kL * (N / 8); e += 128) {
+    const int tt = e / (N / 8), j = e % (N / 8);
+    __nv_bfloat16 hi[8], lo[8];
+    if (tt < cnt) {
+      const uint4 v = *reinterpret_cast<const uint4*>(xbc + (size_t)(tc + tt) * stride + inner + (size_t)g * N + j * 8);
+      const __nv_bfloat16* b = reinterpret_cast<const __nv_bfloat16*>(&v);
+      const float w = expf(la_end - s_la[tt]) * s_dt[tt];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) split_bf16(__bfloat162float(b[i]) * w, hi[i], lo[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) hi[i] = lo[i] = __float2bfloat16_rn(0.f);
+    }
+    *reinterpret_cast<uint4*>(sBh + tt * LDN + j * 8) = *reinterpret_cast<const uint4*>(hi);
+    *reinterpret_cast<uint4*>(sBl + tt * LDN + j * 8) = *reinterpret_cast<const uint4*>(lo);
+  }
+  for (int e = threadIdx.x; e < kL * (P / 8); e += 128) {
+    const int tt = e % kL, j = e / kL;  // (consecutive threads, consecutive tokens: the transposed stores do not collide)
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tt < cnt) v = *reinterpret_cast<const uint4*>(xbc + (size_t)(tc + tt) * stride + (size_t)h * P + j * 8);
+    const __nv_bfloat16* x = reinterpret_cast<const __nv_bfloat16*>(&v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sXt[(j * 8 + i) * LDL + tt] = x[i];
+  }
+  __syncthreads();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int PW = P / 16;  // bands of 16 value channels; the four warps take them in turn
+  for (int band = warp; band < PW; band += 4) {
+    float acc[N / 8][4];
+#pragma unroll
+    for (int i = 0; i < N / 8; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < kL / 16; ++ks) {
+      unsigned af[4];
+      ldsm_x4(af, sXt + (band * 16 + (lane & 15)) * LDL + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int dn = 0; dn < N / 16; ++dn) {
+        unsigned b[4];
+        const int at = (ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDN + dn * 16 + (lane >> 4) * 8;
+        ldsm_x4_trans(b, sBh + at);
+        mma_16816(acc[2 * dn], af, b[0], b[1]);
+        mma_16816(acc[2 * dn + 1], af, b[2], b[3]);
+        ldsm_x4_trans(b, sBl + at);
+        mma_16816(acc[2 * dn], af, b[0], b[1]);
+        mma_16816(acc[2 * dn + 1], af, b[2], b[3]);
+      }
+    }
+    const int gq = lane >> 2, c2 = (lane & 3) * 2;
+    float* dst = piece_state + ((size_t)blockIdx.z * heads + h) * P * N;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const int pch = band * 16 + gq + r * 8;
+#pragma unroll
+      for (int i = 0; i < N / 8; ++i)
+        *reinterpret_cast<float2*>(dst + (size_t)pch * N + i * 8 + c2) = make_float2(acc[i][2 * r], acc[i][2 * r + 1]);
+    }
+  }
+  if (threadIdx.x == 0) piece_decay[(size_t)blockIdx.z * heads + h] = expf(la_end);
+}
+
+// grid (1, heads, sequences * pieces): y of a piece from its starting state (piece_state, as the carry kernel left it).
+template <int N, int P>
+__global__ void __launch_bounds__(128)
+ssd_piece_out_kernel(const __nv_bfloat16* __restrict__ xbc, const __nv_bfloat16* __restrict__ dt_in, long long dt_stride,
+                     int dt_col, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                     const float* __restrict__ skip, float* __restrict__ y, const int* __restrict__ seq_slot,
+                     const int* __restrict__ cu_new, int heads, int groups, int pieces,
+                     const float* __restrict__ piece_state) {
+  constexpr int LDN = N + 8, LDP = P + 8, KN = N / 16, KP = P / 16;
+  extern __shared__ __align__(16) unsigned char raw[];
+  __nv_bfloat16* sC = reinterpret_cast<__nv_bfloat16*>(raw);  // [kL][LDN]
+  __nv_bfloat16* sB = sC + kL * LDN;                           // [kL][LDN]
+  __nv_bfloat16* sX = sB + kL * LDN;                           // [kL][LDP]
+  __nv_bfloat16* sSh = sX + kL * LDP;                          // [P][LDN]: the starting state, rounded
+  __nv_bfloat16* sSl = sSh + P * LDN;                          //           and what the rounding left
+  __shared__ float s_la[kL], s_dt[kL];
+  const int s = blockIdx.z / pieces, piece = blockIdx.z % pieces, h = blockIdx.y;
+  const int inner = heads * P, gn = groups * N, g = h / (heads / groups);
+  const int t_first = cu_new[s] + piece * kL, cnt = min(kL, cu_new[s + 1] - t_first);
+  if (cnt <= 0) return;
+  if (seq_slot[s] < 0) {
+    for (int e = threadIdx.x; e < cnt * P; e += 128) y[(size_t)(t_first + e / P) * inner + h * P + e % P] = 0.f;
+    return;
+  }
+  const int tc = t_first;
+  const size_t stride = (size_t)inner + 2 * gn;
+  piece_decays(dt_in, dt_stride, dt_col, h, dt_bias[h], -expf(a_log[h]), tc, cnt, s_la, s_dt);
+  for (int e = threadIdx.x; e < kL * (N / 8); e += 128) {
+    const int tt = e / (N / 8), j = e % (N / 8);
+    uint4 b = make_uint4(0, 0, 0, 0), c = make_uint4(0, 0, 0, 0);
+    if (tt < cnt) {
+      const __nv_bfloat16* src = xbc + (size_t)(tc + tt) * stride + inner + (size_t)g * N + j * 8;
+      b = *reinterpret_cast<const uint4*>(src);
+      c = *reinterpret_cast<const uint4*>(src + gn);
+    }
+    *reinterpret_cast<uint4*>(sB + tt * LDN + j * 8) = b;
+    *reinterpret_cast<uint4*>(sC + tt * LDN + j * 8) = c;
+  }
+  for (int e = threadIdx.x; e < kL * (P / 8); e += 128) {
+    const int tt = e / (P / 8), j = e % (P / 8);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tt < cnt) v = *reinterpret_cast<const uint4*>(xbc + (size_t)(tc + tt) * stride + (size_t)h * P + j * 8);
+    *reinterpret_cast<uint4*>(sX + tt * LDP + j * 8) = v;
+  }
+  {
+    const float* src = piece_state + ((size_t)blockIdx.z * heads + h) * P * N;
+    for (int e = threadIdx.x; e < P * (N / 4); e += 128) {
+      const int pch = e / (N / 4), j = e % (N / 4);
+      const float4 v = *reinterpret_cast<const float4*>(src + (size_t)pch * N + j * 4);
+      __nv_bfloat16 hi[4], lo[4];
+      split_bf16(v.x, hi[0], lo[0]);
+      split_bf16(v.y, hi[1], lo[1]);
+      split_bf16(v.z, hi[2], lo[2]);
+      split_bf16(v.w, hi[3], lo[3]);
+      *reinterpret_cast<uint2*>(sSh + pch * LDN + j * 4) = *reinterpret_cast<const uint2*>(hi);
+      *reinterpret_cast<uint2*>(sSl + pch * LDN + j * 4) = *reinterpret_cast<const uint2*>(lo);
+    }
+  }
+  __syncthreads();
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gq = lane >> 2, c2 = (lane & 3) * 2;
+  unsigned cf[KN][4];  // this warp's 16 rows of C
+#pragma unroll
+  for (int ks = 0; ks < KN; ++ks) ldsm_x4(cf[ks], sC + (warp * 16 + (lane & 15)) * LDN + ks * 16 + (lane >> 4) * 8);
+
+  // scores C_t . B_s for the piece's 64 tokens s
+  float sc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) sc[i][j] = 0.f;
+#pragma unroll
+  for (int ks = 0; ks < KN; ++ks) {
+#pragma unroll
+    for (int np = 0; np < 4; ++np) {
+      unsigned b[4];
+      ldsm_x4(b, sB + (np * 16 + (lane & 7) + (lane >> 4) * 8) * LDN + ks * 16 + ((lane >> 3) & 1) * 8);
+      mma_16816(sc[2 * np], cf[ks], b[0], b[1]);
+      mma_16816(sc[2 * np + 1], cf[ks], b[2], b[3]);
+    }
+  }
+  // decayed, causal: m[t][s] = score * exp(la_t - la_s) * dt_s for s <= t; as two bfloat16 terms
+  const int row[2] = {warp * 16 + gq, warp * 16 + gq + 8};
+  const float la_row[2] = {s_la[row[0]], s_la[row[1]]};
+  unsigned mh[4][4], ml[4][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    __nv_bfloat16 hi[4], lo[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int sx = i * 8 + c2 + (j & 1), r = j >> 1;
+      const float m = sx <= row[r] ? sc[i][j] * expf(la_row[r] - s_la[sx]) * s_dt[sx] : 0.f;
+      split_bf16(m, hi[j], lo[j]);
+    }
+    mh[i >> 1][(i & 1) * 2] = pack2(hi[0], hi[1]);
+    mh[i >> 1][(i & 1) * 2 + 1] = pack2(hi[2], hi[3]);
+    ml[i >> 1][(i & 1) * 2] = pack2(lo[0], lo[1]);
+    ml[i >> 1][(i & 1) * 2 + 1] = pack2(lo[2], lo[3]);
+  }
+  float o[2 * KP][4], o2[2 * KP][4];
+#pragma unroll
+  for (int i = 0; i < 2 * KP; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o[i][j] = o2[i][j] = 0.f;
+  // inside the piece: m . X
+#pragma unroll
+  for (int kk = 0; kk < kL / 16; ++kk) {
+#pragma unroll
+    for (int dn = 0; dn < KP; ++dn) {
+      unsigned b[4];
+      ldsm_x4_trans(b, sX + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LDP + dn * 16 + (lane >> 4) * 8);
+      mma_16816(o[2 * dn], mh[kk], b[0], b[1]);
+      mma_16816(o[2 * dn + 1], mh[kk], b[2], b[3]);
+      mma_16816(o[2 * dn], ml[kk], b[0], b[1]);
+      mma_16816(o[2 * dn + 1], ml[kk], b[2], b[3]);
+    }
+  }
+  // from the piece's start: C . S (the state lies transposed, [p][n], as a key matrix would)
+#pragma unroll
+  for (int ks = 0; ks < KN; ++ks) {
+#pragma unroll
+    for (int np = 0; np < KP; ++np) {
+      unsigned b[4];
+      const int at = (np * 16 + (lane & 7) + (lane >> 4) * 8) * LDN + ks * 16 + ((lane >> 3) & 1) * 8;
+      ldsm_x4(b, sSh + at);
+      mma_16816(o2[2 * np], cf[ks], b[0], b[1]);
+      mma_16816(o2[2 * np + 1], cf[ks], b[2], b[3]);
+      ldsm_x4(b, sSl + at);
+      mma_16816(o2[2 * np], cf[ks], b[0], b[1]);
+      mma_16816(o2[2 * np + 1], cf[ks], b[2], b[3]);
+    }
+  }
+  const float D = skip[h];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (row[r] >= cnt) continue;
+    const float from_start = expf(la_row[r]);
+    float* dst = y + (size_t)(tc + row[r]) * inner + (size_t)h * P;
+#pragma unroll
+    for (int i = 0; i < 2 * KP; ++i) {
+      const int pch = i * 8 + c2;
+      const float x0 = __bfloat162float(sX[row[r] * LDP + pch]), x1 = __bfloat162float(sX[row[r] * LDP + pch + 1]);
+      *reinterpret_cast<float2*>(dst + pch) = make_float2(fmaf(D, x0, fmaf(from_start, o2[i][2 * r], o[i][2 * r])),
+                                                         fmaf(D, x1, fmaf(from_start, o2[i][2 * r + 1], o[i][2 * r + 1])));
+    }
+  }
+}
+
+template <int N, int P>
+int launch_pieces(const void* xbc, const void* dt_in, long long dt_stride, int dt_col, const float* dt_bias,
+                  const float* a_log, const float* skip, float* state, float* y, const int* seq_slot, const int* seq_start,
+                  const int* cu_new, int n_seqs, int heads, int groups, int pieces, float* piece_state, float* piece_decay,
+                  cudaStream_t stream) {
+  constexpr int smem_state = (P * (kL + 8) + 2 * kL * (N + 8)) * (int)sizeof(__nv_bfloat16);
+  constexpr int smem_out = (2 * kL * (N + 8) + kL * (P + 8) + 2 * P * (N + 8)) * (int)sizeof(__nv_bfloat16);
+  static bool configured = false;  // per instantiation
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(ssd_piece_state_kernel<N, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_state);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(ssd_piece_out_kernel<N, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_out);
+    if (e != cudaSuccess) return ember_fail("ssd_pieces: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const dim3 grid(1, heads, n_seqs * pieces);
+  ssd_piece_state_kernel<N, P><<<grid, 128, smem_state, stream>>>(
+      (const __nv_bfloat16*)xbc, (const __nv_bfloat16*)dt_in, dt_stride, dt_col, dt_bias, a_log, seq_slot, cu_new, heads,
+      groups, pieces, piece_state, piece_decay);
+  const int per_head = P * N;
+  ssd_carry_kernel<<<dim3((per_head + 255) / 256, heads, n_seqs), 256, 0, stream>>>(
+      state, piece_state, piece_decay, seq_slot, seq_start, cu_new, heads, per_head, pieces, kL);
+  ssd_piece_out_kernel<N, P><<<grid, 128, smem_out, stream>>>((const __nv_bfloat16*)xbc, (const __nv_bfloat16*)dt_in,
+                                                              dt_stride, dt_col, dt_bias, a_log, skip, y, seq_slot, cu_new,
+                                                              heads, groups, pieces, piece_state);
+  EMBER_LAUNCH_OK("ssd_pieces");
   return 0;
 }
 
@@ -447,4 +777,26 @@ EMBER_API int ember_ssd_scan(const void* xbc, const void* dt_in, long long dt_st
     return launch_scan<__nv_bfloat16>(xbc, dt_in, dt_stride, dt_col, dt_bias, a_log, skip, state, y, seq_slot, seq_start,
                                       cu_new, n_seqs, heads, vdim, groups, N, pieces, piece_state, piece_decay, stream);
   return ember_fail("ssd_scan: element type %d", dtype);
+}
+
+// The recurrence of a step of prompts in bfloat16 as matrix products over pieces of 64 tokens (see above).  pieces:
+// ceil(longest sequence's new tokens / ember_ssd_pieces_len()); scratch: ember_ssd_scan_scratch(n_seqs, pieces, ...)
+// floats.  Returns 2, having launched nothing, for sizes without an instantiation: the caller takes ember_ssd_scan.
+EMBER_API int ember_ssd_pieces_len(void) { return kL; }
+EMBER_API int ember_ssd_pieces(const void* xbc, const void* dt_in, long long dt_stride, int dt_col, const float* dt_bias,
+                               const float* a_log, const float* skip, float* state, float* y, const int* seq_slot,
+                               const int* seq_start, const int* cu_new, int n_seqs, int heads, int vdim, int groups, int N,
+                               int pieces, float* scratch, cudaStream_t stream) {
+  EMBER_CHECK(n_seqs > 0 && heads > 0 && groups > 0 && heads % groups == 0 && pieces >= 1 && scratch != nullptr,
+              "ssd_pieces: bad sizes");
+  if (vdim != 64 || (N != 64 && N != 128) || (groups * N) % 8 || dt_stride <= 0) return 2;
+  EMBER_CHECK((long long)n_seqs * pieces <= 65535 && heads <= 65535, "ssd_pieces: %d sequences x %d pieces x %d heads exceed one launch",
+              n_seqs, pieces, heads);
+  float* piece_state = scratch;
+  float* piece_decay = scratch + (size_t)n_seqs * pieces * heads * vdim * N;
+  if (N == 64)
+    return launch_pieces<64, 64>(xbc, dt_in, dt_stride, dt_col, dt_bias, a_log, skip, state, y, seq_slot, seq_start, cu_new,
+                                 n_seqs, heads, groups, pieces, piece_state, piece_decay, stream);
+  return launch_pieces<128, 64>(xbc, dt_in, dt_stride, dt_col, dt_bias, a_log, skip, state, y, seq_slot, seq_start, cu_new,
+                                n_seqs, heads, groups, pieces, piece_state, piece_decay, stream);
 }

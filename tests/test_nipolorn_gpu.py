@@ -134,6 +134,46 @@ def test_convolution_recurrence_and_gated_norm_over_steps(ops, dtype, heads, vdi
         close(torch.cat([g[2] for g in got[s]]), P.gated_group_norm(y_used, proj[:, :inner], f64(nw), parts, 1e-6), OP_TOL[dtype])
 
 
+@pytest.mark.parametrize("N, groups", [(128, 1), (64, 3)])
+def test_the_recurrence_as_matrix_products_over_pieces(ops, N, groups):
+    """Prompts in bfloat16 with 64 value channels and 64 or 128 states run as tensor-core products over pieces of 64
+    tokens: unequal sequences, continued from carried state, piece edges inside and at the end of a sequence;
+    against the plain recurrence and against the scalar scan on the same rows."""
+    heads, vdim = 3, 64
+    inner, gn = heads * vdim, groups * N
+    dtb, alog, skip = rnd(3, heads, scale=0.5) - 1, rnd(4, heads, scale=0.5) - 0.5, rnd(5, heads) + 1
+    lengths = {0: 300, 1: 70, 2: 200, 3: 129}
+    xbc = {s: rnd(20 + s, n, inner + 2 * gn).bfloat16() for s, n in lengths.items()}
+    dt = {s: rnd(30 + s, n, 8 + heads).bfloat16() for s, n in lengths.items()}
+    states = {form: torch.full((4, heads, vdim, N), float("nan")).cuda() for form in (True, False)}
+    got = {form: {s: [] for s in lengths} for form in (True, False)}
+    at = {s: 0 for s in lengths}
+    for step in ([(0, 150), (1, 70), (2, 1), (3, 64)], [(2, 199), (0, 150), (3, 65)]):
+        seqs = [(s, at[s], n) for s, n in step]
+        plan = plan_of(seqs)
+        rows = torch.cat([xbc[s][at[s]:at[s] + n] for s, n in step]).cuda()
+        steps_ = torch.cat([dt[s][at[s]:at[s] + n] for s, n in step]).cuda()
+        for form in (True, False):
+            before = ops.launches
+            y = ops.ssd_scan(rows, steps_, 8, dtb.cuda(), alog.cuda(), skip.cuda(), states[form], plan, heads, vdim, groups, N,
+                             tensor_cores=form)
+            assert ops.launches - before == (3 if form else 1) or not form
+            row = 0
+            for s, n in step:
+                got[form][s].append(y[row:row + n])
+                row += n
+        for s, n in step:
+            at[s] += n
+    for s, n in lengths.items():
+        d = P.softplus(f64(dt[s][:, 8:]) + f64(dtb))
+        rows = f64(xbc[s])
+        want = P.ssd_recurrence(rows[:, :inner], rows[:, inner:inner + gn], rows[:, inner + gn:], d, f64(alog), f64(skip),
+                                heads, vdim, groups, N)
+        close(torch.cat(got[False][s]), want, 3e-5)
+        close(torch.cat(got[True][s]), want, 1e-4)
+    close(states[True], f64(states[False]), 1e-4)
+
+
 def test_the_recurrence_remembers_a_token_from_far_back(ops):
     """Decay close to one: a single large input 600 tokens back is what the output is made of."""
     heads, vdim, N, T = 1, 16, 8, 640
@@ -222,11 +262,11 @@ def test_attention_with_window_and_kept_first_tokens(ops, dtype, heads, kv, hd, 
 def test_one_marked_key_is_seen_exactly_where_the_rule_says(ops, dtype, prompt):
     """One key matches the queries strongly and carries a value of 100: the output of a query is about 100 if
     the rule lets it see that key and near 0 if not.  The marked key is placed at the last kept position, the
-    first position that is not kept, and far back; queries just inside and just outside the window, in a
+    first position that is not kept, at a page's edge, and far back; queries just inside and just outside the window, in a
     prompt's rows and in rows decoded one by one."""
     heads, kv, hd, window, keep = 2, 1, 32, 96, 6
     T = 330
-    for marked in (0, keep - 1, keep, 100, 191):
+    for marked in (0, keep - 1, keep, 63, 64, 100, 191):       # (63 | 64: a page's last and first row)
         def qkv_of(_):
             qkv = rnd(marked, T, (heads + 2 * kv) * hd, scale=0.1)
             qkv[:, :heads * hd] += 6.0 * torch.ones(hd).repeat(heads)               # every query points along ones
