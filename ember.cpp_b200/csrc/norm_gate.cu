@@ -2,7 +2,10 @@
 //
 // Everything here is float32 arithmetic on rows: statistics, sums and products are float32 whatever
 // the element type of the rows that go in or come out.  A row is summed by one block in an order
-// that depends on its length alone, so a row's result does not depend on the batch it is in.
+// that depends on its length alone, so a row's result does not depend on the batch it is in.  The kernels are
+// launched for programmatic dependent launch like the step's other small kernels: each lets the kernel after it
+// be scheduled at once and waits for the kernel in front before it touches anything; what that kernel wrote is
+// read through plain pointers, never through the read-only path (see pdl_wait in common.cuh).
 #include "common.cuh"
 
 namespace {
@@ -26,9 +29,11 @@ __device__ __forceinline__ float sigmoidf(float v) { return 1.0f / (1.0f + expf(
 // out = x / sqrt(mean(x^2) + eps) * (offset + w)
 template <typename TOUT>
 __global__ void __launch_bounds__(kThreads)
-rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOUT* __restrict__ out, int d, float eps,
+rmsnorm_kernel(const float* x, const float* __restrict__ w, TOUT* __restrict__ out, int d, float eps,
                float offset) {
   __shared__ float red[kThreads / 32];
+  pdl_trigger();
+  pdl_wait();
   const float* row = x + (size_t)blockIdx.x * d;
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += kThreads) {
@@ -58,6 +63,8 @@ __device__ __forceinline__ float weighted(const Branches& b, size_t row, int i) 
 __global__ void __launch_bounds__(kThreads)
 add_normed_kernel(float* __restrict__ x, const Branches b, const float* __restrict__ w, int d, float eps, float offset) {
   __shared__ float red[kThreads / 32];
+  pdl_trigger();
+  pdl_wait();
   const size_t row = blockIdx.x;
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += kThreads) {
@@ -73,8 +80,10 @@ add_normed_kernel(float* __restrict__ x, const Branches b, const float* __restri
 //   kind 0: g * sigmoid(g) * u
 //   kind 1: g = min(g, limit), u = clamp(u, -limit, limit): g * sigmoid(alpha * g) * (u + shift)
 template <typename T>
-__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total, int n, int kind,
+__global__ void gated_act_kernel(const T* gu, T* __restrict__ out, size_t total, int n, int kind,
                                  float limit, float alpha, float shift) {
+  pdl_trigger();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / n;
     const int c = (int)(i % n);
@@ -95,9 +104,11 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 // y float32 [T, n]; z: n columns of a wider matrix (row stride z_stride).  grid (T, parts).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
+gated_group_norm_kernel(const float* y, const T* z, long long z_stride,
                         const float* __restrict__ w, T* __restrict__ out, int n, int part, float eps) {
   __shared__ float red[kThreads / 32];
+  pdl_trigger();
+  pdl_wait();
   const size_t t = blockIdx.x;
   const int c0 = blockIdx.y * part;
   const float* yr = y + t * n + c0;
@@ -121,13 +132,14 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
 EMBER_API int ember_rmsnorm(const float* x, const float* w, void* out, int rows, int d, float eps, float offset,
                             int out_dtype, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && d > 0, "rmsnorm: %d rows of %d", rows, d);
+  cudaError_t e;
   if (out_dtype == EMBER_F32)
-    rmsnorm_kernel<float><<<rows, kThreads, 0, stream>>>(x, w, (float*)out, d, eps, offset);
+    e = launch_pdl(rmsnorm_kernel<float>, dim3(rows), dim3(kThreads), 0, stream, x, w, (float*)out, d, eps, offset);
   else if (out_dtype == EMBER_BF16)
-    rmsnorm_kernel<__nv_bfloat16><<<rows, kThreads, 0, stream>>>(x, w, (__nv_bfloat16*)out, d, eps, offset);
+    e = launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(kThreads), 0, stream, x, w, (__nv_bfloat16*)out, d, eps, offset);
   else
     return ember_fail("rmsnorm: element type %d", out_dtype);
-  EMBER_LAUNCH_OK("rmsnorm");
+  if (e != cudaSuccess) return ember_fail("rmsnorm: %s", cudaGetErrorString(e));
   return 0;
 }
 
@@ -144,8 +156,8 @@ EMBER_API int ember_add_normed(float* x, const void* const* rows, const long lon
     b.stride[k] = strides[k];
     b.factor[k] = factors[k];
   }
-  add_normed_kernel<<<n_rows, kThreads, 0, stream>>>(x, b, w, d, eps, offset);
-  EMBER_LAUNCH_OK("add_normed");
+  const cudaError_t e = launch_pdl(add_normed_kernel, dim3(n_rows), dim3(kThreads), 0, stream, x, b, w, d, eps, offset);
+  if (e != cudaSuccess) return ember_fail("add_normed: %s", cudaGetErrorString(e));
   return 0;
 }
 
@@ -154,14 +166,16 @@ EMBER_API int ember_gated_act(const void* gu, void* out, int rows, int n, int ki
   EMBER_CHECK(rows > 0 && n > 0 && (kind == 0 || kind == 1), "gated_act: %d rows of %d, kind %d", rows, n, kind);
   const size_t total = (size_t)rows * n;
   const int grid = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
+  cudaError_t e;
   if (dtype == EMBER_F32)
-    gated_act_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, total, n, kind, limit, alpha, shift);
+    e = launch_pdl(gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gu, (float*)out, total, n, kind,
+                   limit, alpha, shift);
   else if (dtype == EMBER_BF16)
-    gated_act_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, n, kind,
-                                                              limit, alpha, shift);
+    e = launch_pdl(gated_act_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+                   (__nv_bfloat16*)out, total, n, kind, limit, alpha, shift);
   else
     return ember_fail("gated_act: element type %d", dtype);
-  EMBER_LAUNCH_OK("gated_act");
+  if (e != cudaSuccess) return ember_fail("gated_act: %s", cudaGetErrorString(e));
   return 0;
 }
 
@@ -170,13 +184,15 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
   EMBER_CHECK(rows > 0 && n > 0 && parts > 0 && n % parts == 0, "gated_group_norm: %d rows of %d in %d parts", rows, n, parts);
   EMBER_CHECK(parts <= 65535, "gated_group_norm: %d parts exceed one launch", parts);
   const dim3 grid(rows, parts);
+  cudaError_t e;
   if (dtype == EMBER_F32)
-    gated_group_norm_kernel<float><<<grid, kThreads, 0, stream>>>(y, (const float*)z, z_stride, w, (float*)out, n, n / parts, eps);
+    e = launch_pdl(gated_group_norm_kernel<float>, grid, dim3(kThreads), 0, stream, y, (const float*)z, z_stride, w,
+                   (float*)out, n, n / parts, eps);
   else if (dtype == EMBER_BF16)
-    gated_group_norm_kernel<__nv_bfloat16><<<grid, kThreads, 0, stream>>>(y, (const __nv_bfloat16*)z, z_stride, w,
-                                                                          (__nv_bfloat16*)out, n, n / parts, eps);
+    e = launch_pdl(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(kThreads), 0, stream, y, (const __nv_bfloat16*)z,
+                   z_stride, w, (__nv_bfloat16*)out, n, n / parts, eps);
   else
     return ember_fail("gated_group_norm: element type %d", dtype);
-  EMBER_LAUNCH_OK("gated_group_norm");
+  if (e != cudaSuccess) return ember_fail("gated_group_norm: %s", cudaGetErrorString(e));
   return 0;
 }

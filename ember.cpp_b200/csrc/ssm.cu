@@ -98,9 +98,11 @@ __global__ void conv_state_kernel(const T* __restrict__ in, long long in_stride,
 
 // One token per sequence (token t is sequence t): the convolution and the state's shift in one launch.
 template <typename T>
-__global__ void conv_step_kernel(const T* __restrict__ in, long long in_stride, int col0, int channels, int taps,
+__global__ void conv_step_kernel(const T* in, long long in_stride, int col0, int channels, int taps,
                                  const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ state,
                                  T* __restrict__ out, const int* __restrict__ seq_slot, const int* __restrict__ seq_start) {
+  pdl_trigger();
+  pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const int t = blockIdx.x;
@@ -168,12 +170,14 @@ __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* src, 
 // multiples of the 16-byte piece), else value by value.
 template <typename T, int RMAX, bool VEC>
 __global__ void __launch_bounds__(kScanThreads)
-ssd_scan_kernel(const T* __restrict__ xbc, const T* __restrict__ dt_in, long long dt_stride, int dt_col,
+ssd_scan_kernel(const T* xbc, const T* dt_in, long long dt_stride, int dt_col,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
                 float* __restrict__ state, float* __restrict__ y, const int* __restrict__ seq_slot,
                 const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads, int vdim, int groups,
                 int N, int stage, int mode, int pieces, float* __restrict__ piece_state, float* __restrict__ piece_decay) {
   extern __shared__ __align__(16) float sm[];
+  pdl_trigger();
+  pdl_wait();
   const int R = (N + kLanes - 1) / kLanes;
   const int row = kLanes * R;          // padded length of a token's B (or C)
   float* sB = sm;                      // [stage][row]
@@ -324,12 +328,26 @@ __global__ void ssd_carry_kernel(float* __restrict__ state, float* __restrict__ 
   const int n_pieces = min(pieces, (cu_new[s + 1] - cu_new[s] + piece_len - 1) / piece_len);
   float* st = state + ((size_t)slot * heads + h) * per_head + e;
   float S = seq_start[s] > 0 ? *st : 0.f;
-  for (int i = 0; i < n_pieces; ++i) {
-    const size_t at = (size_t)s * pieces + i;
-    float* ps = piece_state + (at * heads + h) * per_head + e;
-    const float local = *ps;
-    *ps = S;
-    S = fmaf(piece_decay[at * heads + h], S, local);
+  // eight pieces at a time: their values are asked for together (one trip to memory, not eight), then chained
+  constexpr int kBatch = 8;
+  const size_t step = (size_t)heads * per_head;
+  float* ps = piece_state + ((size_t)s * pieces * heads + h) * per_head + e;
+  const float* pd = piece_decay + (size_t)s * pieces * heads + h;
+  for (int i0 = 0; i0 < n_pieces; i0 += kBatch) {
+    float local[kBatch], decay[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const bool in = i0 + k < n_pieces;
+      local[k] = in ? __ldcs(ps + (size_t)(i0 + k) * step) : 0.f;
+      decay[k] = in ? pd[(size_t)(i0 + k) * heads] : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      if (i0 + k < n_pieces) {
+        ps[(size_t)(i0 + k) * step] = S;
+        S = fmaf(decay[k], S, local[k]);
+      }
+    }
   }
   *st = S;
 }
@@ -351,11 +369,11 @@ int launch_scan(const void* xbc, const void* dt_in, long long dt_stride, int dt_
 #define EMBER_SCAN_MODE(RMAX, MODE)                                                                                    \
   do {                                                                                                                 \
     if (vec)                                                                                                           \
-      ssd_scan_kernel<T, RMAX, true><<<grid, kScanThreads, smem, stream>>>(EMBER_SCAN_ARGS, MODE, pieces, piece_state, \
-                                                                           piece_decay);                              \
+      launch_pdl(ssd_scan_kernel<T, RMAX, true>, grid, dim3(kScanThreads), smem, stream, EMBER_SCAN_ARGS, MODE, pieces, \
+                 piece_state, piece_decay);                                                                           \
     else                                                                                                               \
-      ssd_scan_kernel<T, RMAX, false><<<grid, kScanThreads, smem, stream>>>(EMBER_SCAN_ARGS, MODE, pieces, piece_state, \
-                                                                            piece_decay);                             \
+      launch_pdl(ssd_scan_kernel<T, RMAX, false>, grid, dim3(kScanThreads), smem, stream, EMBER_SCAN_ARGS, MODE, pieces, \
+                 piece_state, piece_decay);                                                                           \
   } while (0)
 #define EMBER_SCAN(MODE)                 \
   do {                                   \
@@ -472,6 +490,7 @@ ssd_piece_state_kernel(const __nv_bfloat16* __restrict__ xbc, const __nv_bfloat1
   piece_decays(dt_in, dt_stride, dt_col, h, dt_bias[h], -expf(a_log[h]), tc, cnt, s_la, s_dt);
   __syncthreads();
   const float la_end = s_la[kL - 1];
+#pragma unroll 4
   for (int e = threadIdx.x; e < kL * (N / 8); e += 128) {
     const int tt = e / (N / 8), j = e % (N / 8);
     __nv_bfloat16 hi[8], lo[8];
@@ -561,6 +580,7 @@ ssd_piece_out_kernel(const __nv_bfloat16* __restrict__ xbc, const __nv_bfloat16*
   const int tc = t_first;
   const size_t stride = (size_t)inner + 2 * gn;
   piece_decays(dt_in, dt_stride, dt_col, h, dt_bias[h], -expf(a_log[h]), tc, cnt, s_la, s_dt);
+#pragma unroll 4
   for (int e = threadIdx.x; e < kL * (N / 8); e += 128) {
     const int tt = e / (N / 8), j = e % (N / 8);
     uint4 b = make_uint4(0, 0, 0, 0), c = make_uint4(0, 0, 0, 0);
@@ -580,6 +600,7 @@ ssd_piece_out_kernel(const __nv_bfloat16* __restrict__ xbc, const __nv_bfloat16*
   }
   {
     const float* src = piece_state + ((size_t)blockIdx.z * heads + h) * P * N;
+#pragma unroll 4
     for (int e = threadIdx.x; e < P * (N / 4); e += 128) {
       const int pch = e / (N / 4), j = e % (N / 4);
       const float4 v = *reinterpret_cast<const float4*>(src + (size_t)pch * N + j * 4);
@@ -730,8 +751,8 @@ EMBER_API int ember_conv_silu(const void* in, long long in_stride, int col0, int
 #define EMBER_CONV(TT)                                                                                                    \
   do {                                                                                                                    \
     if (all_single && T == n_seqs) {                                                                                      \
-      conv_step_kernel<TT><<<dim3(T, bx), 128, 0, stream>>>((const TT*)in, in_stride, col0, channels, taps, w, bias,      \
-                                                            state, (TT*)out, seq_slot, seq_start);                        \
+      launch_pdl(conv_step_kernel<TT>, dim3(T, bx), dim3(128), 0, stream, (const TT*)in, in_stride, col0, channels, taps, \
+                 w, bias, state, (TT*)out, seq_slot, seq_start);                                                          \
     } else if (taps <= 4) {                                                                                               \
       conv_silu_kernel<TT, 4><<<dim3(n_seqs * runs, bx), 128, 0, stream>>>(                                               \
           (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs);   \
