@@ -231,7 +231,7 @@ def design_configs(size: str):
     left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
             "mask": {"size": z["window"], "keep_first": z["keep"]}}
     right = {"heads": z["m_heads"], "vdim": z["m_vdim"], "groups": z["m_groups"], "state": z["m_state"], "conv": 4, "norm_groups": z["m_groups"]}
-    mixer = {"left": left, "right": right, "left_scale": 0.6, "right_scale": 0.9}
+    mixer = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 1.0}
     moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["shared_ff"]}}
     layers = [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0} if i == 0 else moe}
               for i in range(z["layers"])]
@@ -269,7 +269,8 @@ def design_mode(args) -> int:
         record = {"model": config.architecture, "size": args.design_size, "parameters": n_params, "prompt_len": prompt_len, "batch": B,
                   "dtype": "bf16", "data": "synthetic", "peaks": pk}
         for timing in (False, True):
-            opt = E.RuntimeOptions(dtype="bfloat16", max_tokens=(B + 1) * (prompt_len + K + W + 128), op_timing=timing)
+            opt = E.RuntimeOptions.from_env(E.RuntimeOptions(dtype="bfloat16", max_tokens=(B + 1) * (prompt_len + K + W + 128),
+                                                             op_timing=timing))       # (EMBER_* switches apply on top)
             eng = Engine.from_spec(spec, tensors, options=opt)
             vocab = spec.vocab_size
             prompt = rng.integers(0, vocab, prompt_len).tolist()

@@ -19,16 +19,14 @@ constexpr int kChunkKeys = 32 * kWarps;
 // PER: query heads a key/value head (rounded up); DPL: value dims a lane (vd <= 32 * DPL, vd % DPL == 0)
 template <int PER, int DPL>
 __global__ void __launch_bounds__(32 * kWarps)
-decode_kept_partial_kernel(const __nv_bfloat16* qkv, const __nv_bfloat16* kc, const __nv_bfloat16* vc,
-                           float* __restrict__ part,
+decode_kept_partial_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ kc,
+                           const __nv_bfloat16* __restrict__ vc, float* __restrict__ part,
                            const int* __restrict__ positions, const int* __restrict__ seq_slot,
                            const int* __restrict__ pages, int max_blocks, int n_heads, int kv_heads, int hd, int vd,
                            float scale, int window, int keep_first, int n_chunks) {
   __shared__ float q_s[PER][256];
   __shared__ float m_s[kWarps][PER], l_s[kWarps][PER];
   __shared__ float acc_s[kWarps][PER][32 * DPL];
-  pdl_trigger();
-  pdl_wait();
   const int c = blockIdx.x, g = blockIdx.y, t = blockIdx.z;
   const int per = n_heads / kv_heads;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -166,10 +164,8 @@ decode_kept_partial_kernel(const __nv_bfloat16* qkv, const __nv_bfloat16* kc, co
 }
 
 // grid (T * n_heads): out = sum_c e^(m_c - M) acc_c / sum_c e^(m_c - M) l_c, chunks in order
-__global__ void decode_kept_merge_kernel(const float* part, __nv_bfloat16* __restrict__ out,
+__global__ void decode_kept_merge_kernel(const float* __restrict__ part, __nv_bfloat16* __restrict__ out,
                                          const int* __restrict__ seq_slot, int n_heads, int vd, int n_chunks) {
-  pdl_trigger();
-  pdl_wait();
   const int item = blockIdx.x, t = item / n_heads;
   __nv_bfloat16* o = out + (size_t)item * vd;
   if (seq_slot[t] < 0) {
@@ -200,7 +196,7 @@ template <int PER, int DPL>
 void launch_partial(dim3 grid, cudaStream_t stream, const void* qkv, const void* kc, const void* vc, float* part,
                     const int* positions, const int* seq_slot, const int* pages, int max_blocks, int n_heads,
                     int kv_heads, int hd, int vd, float scale, int window, int keep_first, int n_chunks) {
-  launch_pdl(decode_kept_partial_kernel<PER, DPL>, grid, dim3(32 * kWarps), 0, stream, (const __nv_bfloat16*)qkv,
+  launch_plain(decode_kept_partial_kernel<PER, DPL>, grid, dim3(32 * kWarps), 0, stream, (const __nv_bfloat16*)qkv,
              (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, part, positions, seq_slot, pages, max_blocks, n_heads,
              kv_heads, hd, vd, scale, window, keep_first, n_chunks);
 }
@@ -251,7 +247,7 @@ EMBER_API int ember_attention_decode_kept(const void* qkv, const void* kc, const
 #undef EMBER_KEPT_PER
 #undef EMBER_KEPT
   EMBER_LAUNCH_OK("attention_decode_kept");
-  launch_pdl(decode_kept_merge_kernel, dim3(T * n_heads), dim3(vd <= 32 ? 32 : (vd <= 64 ? 64 : 128)), 0, stream,
+  launch_plain(decode_kept_merge_kernel, dim3(T * n_heads), dim3(vd <= 32 ? 32 : (vd <= 64 ? 64 : 128)), 0, stream,
              (const float*)scratch, (__nv_bfloat16*)out, seq_slot, n_heads, vd, n_chunks);
   EMBER_LAUNCH_OK("attention_decode_kept (merge)");
   return 0;

@@ -194,6 +194,16 @@ inline size_t spread_smem(size_t need, long long blocks) {
   const size_t want = room > 8192 ? room - 6144 : 0;  // less a block's own kilobyte of the SM's shared memory and its static variables
   return want > need ? want : need;
 }
+// An ordinary launch with launch_pdl's shape: the kernel begins when everything before it in the stream has ended.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_plain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 template <typename... KArgs, typename... Args>
 cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};

@@ -17,11 +17,9 @@ namespace {
 
 // ---------------------------------------------------------------------------- routing
 __global__ void __launch_bounds__(1024)
-moe_route_kernel(const int* tokens, const int* __restrict__ table, int n_pairs, int top, int experts,
+moe_route_kernel(const int* __restrict__ tokens, const int* __restrict__ table, int n_pairs, int top, int experts,
                  int vocab, int* __restrict__ pair_expert, int* __restrict__ offsets, int* __restrict__ sorted) {
   extern __shared__ int sm_i[];  // count[experts], cursor[experts]
-  pdl_trigger();
-  pdl_wait();
   int* count = sm_i;
   int* cursor = sm_i + experts;
   for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
@@ -76,10 +74,8 @@ constexpr int kStreamOutputs = 4;  // per warp
 // grid (pairs, ceil(inner / 32))
 template <typename T>
 __global__ void __launch_bounds__(kStreamWarps * 32)
-moe_gate_up_stream_kernel(const T* a, const T* __restrict__ w, const int* pair_expert,
+moe_gate_up_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ pair_expert,
                           T* __restrict__ out, int top, int width, int inner) {
-  pdl_trigger();
-  pdl_wait();
   const int q = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* row = a + (size_t)(q / top) * width;
   const T* we = w + (size_t)pair_expert[q] * 2 * inner * width;
@@ -95,10 +91,8 @@ moe_gate_up_stream_kernel(const T* a, const T* __restrict__ w, const int* pair_e
 // grid (pairs, ceil(width / 32))
 template <typename T>
 __global__ void __launch_bounds__(kStreamWarps * 32)
-moe_down_stream_kernel(const T* a, const T* __restrict__ w, const int* pair_expert,
+moe_down_stream_kernel(const T* __restrict__ a, const T* __restrict__ w, const int* __restrict__ pair_expert,
                        float* __restrict__ out, int width, int inner) {
-  pdl_trigger();
-  pdl_wait();
   const int q = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* row = a + (size_t)q * inner;
   const T* we = w + (size_t)pair_expert[q] * width * inner;
@@ -306,7 +300,7 @@ EMBER_API int ember_moe_route(const int* tokens, const int* table, int T, int to
   EMBER_CHECK(T > 0 && top > 0 && experts > 0 && vocab > 0 && top <= experts, "moe_route: bad sizes");
   EMBER_CHECK(experts <= 4096, "moe_route: %d experts (at most 4096)", experts);
   EMBER_CHECK((long long)T * top < (1ll << 30), "moe_route: %d tokens x %d choices", T, top);
-  const cudaError_t e = launch_pdl(moe_route_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(int), stream, tokens, table,
+  const cudaError_t e = launch_plain(moe_route_kernel, dim3(1), dim3(1024), 2 * experts * sizeof(int), stream, tokens, table,
                                    T * top, top, experts, vocab, pair_expert, offsets, sorted);
   if (e != cudaSuccess) return ember_fail("moe_route: %s", cudaGetErrorString(e));
   return 0;
@@ -328,10 +322,10 @@ EMBER_API int ember_moe_gate_up(const void* a, const void* w, const int* pair_ex
   EMBER_CHECK(grid.y <= 65535, "moe_gate_up: %d outputs exceed one launch", inner);
   cudaError_t e;
   if (dtype == EMBER_F32)
-    e = launch_pdl(moe_gate_up_stream_kernel<float>, grid, dim3(kStreamWarps * 32), 0, stream, (const float*)a, (const float*)w,
+    e = launch_plain(moe_gate_up_stream_kernel<float>, grid, dim3(kStreamWarps * 32), 0, stream, (const float*)a, (const float*)w,
                    pair_expert, (float*)out, top, width, inner);
   else if (dtype == EMBER_BF16)
-    e = launch_pdl(moe_gate_up_stream_kernel<__nv_bfloat16>, grid, dim3(kStreamWarps * 32), 0, stream, (const __nv_bfloat16*)a,
+    e = launch_plain(moe_gate_up_stream_kernel<__nv_bfloat16>, grid, dim3(kStreamWarps * 32), 0, stream, (const __nv_bfloat16*)a,
                    (const __nv_bfloat16*)w, pair_expert, (__nv_bfloat16*)out, top, width, inner);
   else
     return ember_fail("moe_gate_up: element type %d", dtype);
@@ -354,10 +348,10 @@ EMBER_API int ember_moe_down(const void* a, const void* w, const int* pair_exper
   EMBER_CHECK(grid.y <= 65535, "moe_down: %d outputs exceed one launch", width);
   cudaError_t e;
   if (dtype == EMBER_F32)
-    e = launch_pdl(moe_down_stream_kernel<float>, grid, dim3(kStreamWarps * 32), 0, stream, (const float*)a, (const float*)w,
+    e = launch_plain(moe_down_stream_kernel<float>, grid, dim3(kStreamWarps * 32), 0, stream, (const float*)a, (const float*)w,
                    pair_expert, out, width, inner);
   else if (dtype == EMBER_BF16)
-    e = launch_pdl(moe_down_stream_kernel<__nv_bfloat16>, grid, dim3(kStreamWarps * 32), 0, stream, (const __nv_bfloat16*)a,
+    e = launch_plain(moe_down_stream_kernel<__nv_bfloat16>, grid, dim3(kStreamWarps * 32), 0, stream, (const __nv_bfloat16*)a,
                    (const __nv_bfloat16*)w, pair_expert, out, width, inner);
   else
     return ember_fail("moe_down: element type %d", dtype);

@@ -3,9 +3,11 @@
 // Everything here is float32 arithmetic on rows: statistics, sums and products are float32 whatever
 // the element type of the rows that go in or come out.  A row is summed by one block in an order
 // that depends on its length alone, so a row's result does not depend on the batch it is in.  The kernels are
-// launched for programmatic dependent launch like the step's other small kernels: each lets the kernel after it
-// be scheduled at once and waits for the kernel in front before it touches anything; what that kernel wrote is
-// read through plain pointers, never through the read-only path (see pdl_wait in common.cuh).
+// launched the ordinary way.  Programmatic dependent launch was tried for all the small kernels of this file, of
+// ssm.cu, moe.cu and attention_decode_kept.cu and lost: a one-token step of four layers took 0.757 ms with ordinary
+// launches, 0.865 ms with every kernel waiting for the one in front and releasing its follower at once, and 0.903 ms
+// with the wait alone.  Several of these kernels run in more than one wave of blocks, and blocks that sit on the SMs
+// waiting take the room of the waves that should run.
 #include "common.cuh"
 
 namespace {
@@ -29,11 +31,9 @@ __device__ __forceinline__ float sigmoidf(float v) { return 1.0f / (1.0f + expf(
 // out = x / sqrt(mean(x^2) + eps) * (offset + w)
 template <typename TOUT>
 __global__ void __launch_bounds__(kThreads)
-rmsnorm_kernel(const float* x, const float* __restrict__ w, TOUT* __restrict__ out, int d, float eps,
+rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TOUT* __restrict__ out, int d, float eps,
                float offset) {
   __shared__ float red[kThreads / 32];
-  pdl_trigger();
-  pdl_wait();
   const float* row = x + (size_t)blockIdx.x * d;
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += kThreads) {
@@ -63,8 +63,6 @@ __device__ __forceinline__ float weighted(const Branches& b, size_t row, int i) 
 __global__ void __launch_bounds__(kThreads)
 add_normed_kernel(float* __restrict__ x, const Branches b, const float* __restrict__ w, int d, float eps, float offset) {
   __shared__ float red[kThreads / 32];
-  pdl_trigger();
-  pdl_wait();
   const size_t row = blockIdx.x;
   float ss = 0.f;
   for (int i = threadIdx.x; i < d; i += kThreads) {
@@ -80,10 +78,8 @@ add_normed_kernel(float* __restrict__ x, const Branches b, const float* __restri
 //   kind 0: g * sigmoid(g) * u
 //   kind 1: g = min(g, limit), u = clamp(u, -limit, limit): g * sigmoid(alpha * g) * (u + shift)
 template <typename T>
-__global__ void gated_act_kernel(const T* gu, T* __restrict__ out, size_t total, int n, int kind,
+__global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, size_t total, int n, int kind,
                                  float limit, float alpha, float shift) {
-  pdl_trigger();
-  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const size_t row = i / n;
     const int c = (int)(i % n);
@@ -104,11 +100,9 @@ __global__ void gated_act_kernel(const T* gu, T* __restrict__ out, size_t total,
 // y float32 [T, n]; z: n columns of a wider matrix (row stride z_stride).  grid (T, parts).
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-gated_group_norm_kernel(const float* y, const T* z, long long z_stride,
+gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
                         const float* __restrict__ w, T* __restrict__ out, int n, int part, float eps) {
   __shared__ float red[kThreads / 32];
-  pdl_trigger();
-  pdl_wait();
   const size_t t = blockIdx.x;
   const int c0 = blockIdx.y * part;
   const float* yr = y + t * n + c0;
@@ -134,9 +128,9 @@ EMBER_API int ember_rmsnorm(const float* x, const float* w, void* out, int rows,
   EMBER_CHECK(rows > 0 && d > 0, "rmsnorm: %d rows of %d", rows, d);
   cudaError_t e;
   if (out_dtype == EMBER_F32)
-    e = launch_pdl(rmsnorm_kernel<float>, dim3(rows), dim3(kThreads), 0, stream, x, w, (float*)out, d, eps, offset);
+    e = launch_plain(rmsnorm_kernel<float>, dim3(rows), dim3(kThreads), 0, stream, x, w, (float*)out, d, eps, offset);
   else if (out_dtype == EMBER_BF16)
-    e = launch_pdl(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(kThreads), 0, stream, x, w, (__nv_bfloat16*)out, d, eps, offset);
+    e = launch_plain(rmsnorm_kernel<__nv_bfloat16>, dim3(rows), dim3(kThreads), 0, stream, x, w, (__nv_bfloat16*)out, d, eps, offset);
   else
     return ember_fail("rmsnorm: element type %d", out_dtype);
   if (e != cudaSuccess) return ember_fail("rmsnorm: %s", cudaGetErrorString(e));
@@ -156,7 +150,7 @@ EMBER_API int ember_add_normed(float* x, const void* const* rows, const long lon
     b.stride[k] = strides[k];
     b.factor[k] = factors[k];
   }
-  const cudaError_t e = launch_pdl(add_normed_kernel, dim3(n_rows), dim3(kThreads), 0, stream, x, b, w, d, eps, offset);
+  const cudaError_t e = launch_plain(add_normed_kernel, dim3(n_rows), dim3(kThreads), 0, stream, x, b, w, d, eps, offset);
   if (e != cudaSuccess) return ember_fail("add_normed: %s", cudaGetErrorString(e));
   return 0;
 }
@@ -168,10 +162,10 @@ EMBER_API int ember_gated_act(const void* gu, void* out, int rows, int n, int ki
   const int grid = (int)((total + 255) / 256 < 65535 * 16 ? (total + 255) / 256 : 65535 * 16);
   cudaError_t e;
   if (dtype == EMBER_F32)
-    e = launch_pdl(gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gu, (float*)out, total, n, kind,
+    e = launch_plain(gated_act_kernel<float>, dim3(grid), dim3(256), 0, stream, (const float*)gu, (float*)out, total, n, kind,
                    limit, alpha, shift);
   else if (dtype == EMBER_BF16)
-    e = launch_pdl(gated_act_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
+    e = launch_plain(gated_act_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, (const __nv_bfloat16*)gu,
                    (__nv_bfloat16*)out, total, n, kind, limit, alpha, shift);
   else
     return ember_fail("gated_act: element type %d", dtype);
@@ -186,10 +180,10 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
   const dim3 grid(rows, parts);
   cudaError_t e;
   if (dtype == EMBER_F32)
-    e = launch_pdl(gated_group_norm_kernel<float>, grid, dim3(kThreads), 0, stream, y, (const float*)z, z_stride, w,
+    e = launch_plain(gated_group_norm_kernel<float>, grid, dim3(kThreads), 0, stream, y, (const float*)z, z_stride, w,
                    (float*)out, n, n / parts, eps);
   else if (dtype == EMBER_BF16)
-    e = launch_pdl(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(kThreads), 0, stream, y, (const __nv_bfloat16*)z,
+    e = launch_plain(gated_group_norm_kernel<__nv_bfloat16>, grid, dim3(kThreads), 0, stream, y, (const __nv_bfloat16*)z,
                    z_stride, w, (__nv_bfloat16*)out, n, n / parts, eps);
   else
     return ember_fail("gated_group_norm: element type %d", dtype);

@@ -60,7 +60,8 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, long long in_stride, 
     hist[TMAX - 1 - m] = v;
   }
   const float b = bias[c];
-  for (int i = i0; i < i1; ++i) {
+#pragma unroll 8
+  for (int i = i0; i < i1; ++i) {   // (unrolled: eight tokens' loads are on their way together)
     hist[TMAX - 1] = to_float(src[(size_t)i * in_stride]);
     float acc = b;
 #pragma unroll
@@ -98,11 +99,9 @@ __global__ void conv_state_kernel(const T* __restrict__ in, long long in_stride,
 
 // One token per sequence (token t is sequence t): the convolution and the state's shift in one launch.
 template <typename T>
-__global__ void conv_step_kernel(const T* in, long long in_stride, int col0, int channels, int taps,
+__global__ void conv_step_kernel(const T* __restrict__ in, long long in_stride, int col0, int channels, int taps,
                                  const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ state,
                                  T* __restrict__ out, const int* __restrict__ seq_slot, const int* __restrict__ seq_start) {
-  pdl_trigger();
-  pdl_wait();
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const int t = blockIdx.x;
@@ -170,14 +169,12 @@ __device__ __forceinline__ void load16<__nv_bfloat16>(const __nv_bfloat16* src, 
 // multiples of the 16-byte piece), else value by value.
 template <typename T, int RMAX, bool VEC>
 __global__ void __launch_bounds__(kScanThreads)
-ssd_scan_kernel(const T* xbc, const T* dt_in, long long dt_stride, int dt_col,
+ssd_scan_kernel(const T* __restrict__ xbc, const T* __restrict__ dt_in, long long dt_stride, int dt_col,
                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ skip,
                 float* __restrict__ state, float* __restrict__ y, const int* __restrict__ seq_slot,
                 const int* __restrict__ seq_start, const int* __restrict__ cu_new, int heads, int vdim, int groups,
                 int N, int stage, int mode, int pieces, float* __restrict__ piece_state, float* __restrict__ piece_decay) {
   extern __shared__ __align__(16) float sm[];
-  pdl_trigger();
-  pdl_wait();
   const int R = (N + kLanes - 1) / kLanes;
   const int row = kLanes * R;          // padded length of a token's B (or C)
   float* sB = sm;                      // [stage][row]
@@ -369,10 +366,10 @@ int launch_scan(const void* xbc, const void* dt_in, long long dt_stride, int dt_
 #define EMBER_SCAN_MODE(RMAX, MODE)                                                                                    \
   do {                                                                                                                 \
     if (vec)                                                                                                           \
-      launch_pdl(ssd_scan_kernel<T, RMAX, true>, grid, dim3(kScanThreads), smem, stream, EMBER_SCAN_ARGS, MODE, pieces, \
+      launch_plain(ssd_scan_kernel<T, RMAX, true>, grid, dim3(kScanThreads), smem, stream, EMBER_SCAN_ARGS, MODE, pieces, \
                  piece_state, piece_decay);                                                                           \
     else                                                                                                               \
-      launch_pdl(ssd_scan_kernel<T, RMAX, false>, grid, dim3(kScanThreads), smem, stream, EMBER_SCAN_ARGS, MODE, pieces, \
+      launch_plain(ssd_scan_kernel<T, RMAX, false>, grid, dim3(kScanThreads), smem, stream, EMBER_SCAN_ARGS, MODE, pieces, \
                  piece_state, piece_decay);                                                                           \
   } while (0)
 #define EMBER_SCAN(MODE)                 \
@@ -751,7 +748,7 @@ EMBER_API int ember_conv_silu(const void* in, long long in_stride, int col0, int
 #define EMBER_CONV(TT)                                                                                                    \
   do {                                                                                                                    \
     if (all_single && T == n_seqs) {                                                                                      \
-      launch_pdl(conv_step_kernel<TT>, dim3(T, bx), dim3(128), 0, stream, (const TT*)in, in_stride, col0, channels, taps, \
+      launch_plain(conv_step_kernel<TT>, dim3(T, bx), dim3(128), 0, stream, (const TT*)in, in_stride, col0, channels, taps, \
                  w, bias, state, (TT*)out, seq_slot, seq_start);                                                          \
     } else if (taps <= 4) {                                                                                               \
       conv_silu_kernel<TT, 4><<<dim3(n_seqs * runs, bx), 128, 0, stream>>>(                                               \

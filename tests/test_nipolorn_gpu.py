@@ -242,7 +242,7 @@ def plain_attention_rows(qkv, heads, kv, hd, vd, window, keep, scale):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("heads, kv, hd, vd, window, keep", [(4, 2, 48, 48, 70, 5), (6, 3, 24, 40, 33, 66), (2, 1, 64, 64, 130, 0),
+@pytest.mark.parametrize("heads, kv, hd, vd, window, keep", [(4, 2, 80, 80, 70, 5), (6, 3, 24, 40, 33, 66), (2, 1, 64, 64, 130, 0),
                                                             (4, 4, 32, 32, 64, 64), (2, 2, 16, 16, 1, 1)])
 def test_attention_with_window_and_kept_first_tokens(ops, dtype, heads, kv, hd, vd, window, keep):
     """Prompts of unequal length, portions on top of a cache, one token each; windows shorter and longer than a
@@ -264,7 +264,7 @@ def test_one_marked_key_is_seen_exactly_where_the_rule_says(ops, dtype, prompt):
     the rule lets it see that key and near 0 if not.  The marked key is placed at the last kept position, the
     first position that is not kept, at a page's edge, and far back; queries just inside and just outside the window, in a
     prompt's rows and in rows decoded one by one."""
-    heads, kv, hd, window, keep = 2, 1, 32, 96, 6
+    heads, kv, hd, window, keep = 2, 1, 32, 90, 5
     T = 330
     for marked in (0, keep - 1, keep, 63, 64, 100, 191):       # (63 | 64: a page's last and first row)
         def qkv_of(_):
