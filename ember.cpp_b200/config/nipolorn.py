@@ -66,6 +66,8 @@ class NipolornConfig(ModelConfig):
             for key in ("left.dim", "left.heads", "left.kv_heads", "left.vdim", "left.mask.size", "right.conv", "right.groups",
                         "right.heads", "right.norm_groups", "right.state", "right.vdim"):
                 _get(m, key, int, at + "mixer.")
+            if m["left"]["mask"].get("keep_first") is None:      # a window that keeps no first tokens
+                m["left"]["mask"]["keep_first"] = 0
             _get(m, "left.mask.keep_first", int, at + "mixer.", positive=False)
             if m["left"]["mask"]["keep_first"] < 0:
                 raise ConfigError(f"NipolornConfig: {at}mixer.left.mask.keep_first is negative")

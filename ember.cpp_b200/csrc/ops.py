@@ -215,6 +215,10 @@ class CudaOps:
         # attention: prefill attention with head size 64 on the tcgen05 kernel, or ("mma") on the mma.sync kernel
         #   (which takes every other head size anyway)
         self.attention_tc = options.attention == "tc"
+        # attention_kept_fast: attention with kept first tokens or a value size of its own takes the mma.sync prompt
+        #   kernel and the split one-token kernel where they have the sizes; False takes the plain kernel everywhere
+        #   (a measurement switch: the twin that the two are compared with)
+        self.attention_kept_fast = True
         # op_timing, nvtx: per-launch CUDA events and NVTX ranges (see options.py); both off by default
         self.op_timing, self.nvtx = options.op_timing, options.nvtx
         self._timed = []
@@ -609,7 +613,8 @@ class CudaOps:
             self._call("ember_kv_store_v", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(), plan.positions.data_ptr(),
                        plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.T,
                        n_heads, kv_heads, hd, vd, _code(qkv.dtype))
-        if qkv.dtype == torch.bfloat16 and plan.all_single and plan.T == plan.n:
+        fast = self.attention_kept_fast and qkv.dtype == torch.bfloat16
+        if fast and plan.all_single and plan.T == plan.n:
             # one token each: the visible keys in chunks of 128, a block a chunk and key/value head, then the merge
             max_keys = min(keep_first + window, plan.max_end) if window > 0 else plan.max_end
             scratch = torch.empty(self.lib.ember_attention_decode_kept_scratch(plan.T, n_heads, vd, max_keys),
@@ -621,7 +626,7 @@ class CudaOps:
             if rc == 0:
                 self.launches += 1      # (the merge)
                 return out
-        if qkv.dtype == torch.bfloat16 and vd == hd and scale > 0 and not plan.all_single:
+        if fast and vd == hd and hd % 16 == 0 and hd <= 128 and scale > 0 and not plan.all_single:
             rc = self._call("ember_attention_prefill_kept", qkv.data_ptr(), cache.k.data_ptr(), cache.v.data_ptr(),
                             out.data_ptr(), plan.seq_slot.data_ptr(), plan.seq_start.data_ptr(), plan.seq_new.data_ptr(),
                             plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n, plan.max_new, n_heads,

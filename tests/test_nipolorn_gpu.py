@@ -243,7 +243,7 @@ def plain_attention_rows(qkv, heads, kv, hd, vd, window, keep, scale):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, kv, hd, vd, window, keep", [(4, 2, 80, 80, 70, 5), (6, 3, 24, 40, 33, 66), (2, 1, 64, 64, 130, 0),
-                                                            (4, 4, 32, 32, 64, 64), (2, 2, 16, 16, 1, 1)])
+                                                            (4, 4, 32, 32, 64, 64), (2, 2, 16, 16, 1, 1), (2, 1, 16, 20, 33, 2)])
 def test_attention_with_window_and_kept_first_tokens(ops, dtype, heads, kv, hd, vd, window, keep):
     """Prompts of unequal length, portions on top of a cache, one token each; windows shorter and longer than a
     page, kept tokens within one page and across two; values wider than keys."""
@@ -385,3 +385,42 @@ def test_greedy_generation_through_the_session(folders, plains, dtype):
         else:       # a near tie may fall the other way in bfloat16: the first tokens agree, and most of the rest
             assert [g[0] for g in got] == [w[0] for w in want]
             assert sum(a == b for g, w in zip(got, want) for a, b in zip(g, w)) >= 24
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_replay_of_a_model_folder(folders, plains, tmp_path, dtype):
+    """bin/trace_run picks the model by config.json: each request whole, then most of it in one step and the rest
+    token by token, then unequal requests together, their slots given back at their ends."""
+    from test_replay_gpu import Replay
+    m = plains["nip_b"]
+    vocab = m.cfg["vocab"]
+    seqs = {f"q{i}": U.ids(400 + i, vocab, n) for i, n in enumerate((130, 1, 47))}
+    refs = {k: P.forward(m, s) for k, s in seqs.items()}
+    rp = Replay(folders["nip_b"], dtype, tmp_path, sum(len(s) for s in seqs.values()))
+    for k, s in seqs.items():
+        got = rp.step([(k + "w", s, list(range(len(s))))], end=[k + "w"]).reshape(len(s), vocab)
+        assert U.row_error(got, refs[k]) < U.TOL[dtype]
+    fed = {k: max(1, len(s) - 20) for k, s in seqs.items()}
+    rows = {k: [] for k in seqs}
+    out = rp.step([(k, s[:fed[k]], list(range(fed[k]))) for k, s in seqs.items()], end=[k for k, s in seqs.items() if fed[k] == len(s)])
+    at = 0
+    for k in seqs:
+        rows[k].append(out.reshape(-1, vocab)[at:at + fed[k]])
+        at += fed[k]
+    while any(fed[k] < len(s) for k, s in seqs.items()):
+        live = [k for k, s in seqs.items() if fed[k] < len(s)]
+        out = rp.step([(k, [seqs[k][fed[k]]], [0]) for k in live], end=[k for k in live if fed[k] + 1 == len(seqs[k])]).reshape(-1, vocab)
+        for r, k in enumerate(live):
+            rows[k].append(out[r:r + 1])
+            fed[k] += 1
+    rp.close()
+    for k in seqs:
+        assert U.row_error(np.concatenate(rows[k]), refs[k]) < U.TOL[dtype]
+
+
+@pytest.mark.parametrize("hd, vd", [(40, 40), (8, 8), (24, 16)])
+def test_head_sizes_without_a_tensor_core_kernel_take_the_plain_one_in_bfloat16(ops, hd, vd):
+    data = [rnd(5, 150, (3 + 3) * hd + 3 * vd).bfloat16()]
+    scale = 0.9 / math.sqrt(hd)
+    got = attention_steps(ops, "bfloat16", 3, 3, hd, vd, 40, 2, [[100], [1], [49]], lambda i: data[i], scale)
+    close(got[0], plain_attention_rows(data[0], 3, 3, hd, vd, 40, 2, scale), OP_TOL["bfloat16"])

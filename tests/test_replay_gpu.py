@@ -125,12 +125,14 @@ def test_replay_three_ways(tiny_folders, plains, tmp_path, name, dtype):
 
 
 def test_replay_refuses_more_than_the_cache_holds(tiny_folders, tmp_path):
+    """--max-tokens 64 gives 64 positions plus a partly filled page for each of up to 64 requests: 65 pages."""
     rp = Replay(tiny_folders["tiny_a"], "float32", tmp_path, 64)
-    rp.step([("a", [1] * 60, [59])])
-    rp.proc.stdin.write(json.dumps({"step": 1, "entries": [{"id": "b", "tokens": [1], "want": [0]}], "end": []}) + "\n")
+    rp.step([("a", [1] * 60, [59]), ("b", [1], [0])])          # 61 live tokens in two pages: within what was asked for
+    rp.step([(f"c{i}", [1], []) for i in range(63)])           # 65 pages held
+    rp.proc.stdin.write(json.dumps({"step": 2, "entries": [{"id": "d", "tokens": [1], "want": [0]}], "end": []}) + "\n")
     rp.proc.stdin.flush()
     rp.proc.stdin.close()
-    assert rp.proc.wait(timeout=60) != 0          # the second request needs a page that is not there
+    assert rp.proc.wait(timeout=60) != 0          # one more request needs a page that is not there
 
 
 def test_replay_writes_nothing_where_nothing_is_wanted(tiny_folders, plains, tmp_path):
