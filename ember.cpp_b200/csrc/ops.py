@@ -418,6 +418,8 @@ class CudaOps:
             raise KernelError("linear: the residual is float32 of the output's shape")
         self._dense(a, "linear input")
         self._dense(w, "linear weight")
+        if w.dtype == torch.bfloat16 and K % 8:
+            return self._linear_unaligned(a, w, bias, act, residual, out_dtype)
         if w.dtype == torch.float32:
             out = residual if residual is not None else torch.empty((M, N), dtype=torch.float32, device=a.device)
             self._call("ember_gemm_f32", a.data_ptr(), w.data_ptr(), self._ptr(bias), self._ptr(residual),
@@ -458,6 +460,24 @@ class CudaOps:
         if act == "gelu_erf":
             self._call("ember_act_inplace", out.data_ptr(), out.numel(), _ACT[act], _code(target))
         return out
+
+    def _linear_unaligned(self, a, w, bias, act, residual, out_dtype):
+        """A bfloat16 product whose rows are no multiples of 16 bytes (K % 8 != 0), which none of the bfloat16 kernels
+        reads: the float32 product on the same values (bfloat16 widens exactly, the sums are float32 as theirs are),
+        its result rounded as theirs would be.  Slow; a model of such sizes still runs in both compute types."""
+        wide = getattr(w, "_ember_f32", None)          # kept on the weight itself: made once, dies with it
+        if wide is None or wide.shape != w.shape or wide.device != w.device:
+            wide = w.float()
+            w._ember_f32 = wide
+        rows = a.float()
+        M, K = a.shape
+        N = w.shape[0]
+        out = residual if residual is not None else torch.empty((M, N), dtype=torch.float32, device=a.device)
+        self._call("ember_gemm_f32", rows.data_ptr(), wide.data_ptr(), self._ptr(bias), self._ptr(residual), out.data_ptr(),
+                   M, N, K, _ACT[act])
+        if residual is not None:
+            return out
+        return out.to(out_dtype or torch.bfloat16)
 
     def linear_tc(self, a, w, bias, act, residual, out, tile_n: int = 0):
         """The tcgen05 product with its epilogue (bias, activation, float32 residual sum) into `out`."""
@@ -764,10 +784,11 @@ class CudaOps:
                    pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr())
         return pair_expert, offsets, order, T, top, experts
 
-    def _moe_tiled(self, pairs, dtype, tiled):
+    def _moe_tiled(self, pairs, dtype, tiled, k, n_out):
+        """Tiles from MOE_TILE_PAIRS pairs on in bfloat16, where rows are whole 16-byte pieces and outputs come in twos."""
         if tiled is None:
             tiled = dtype == torch.bfloat16 and pairs >= MOE_TILE_PAIRS
-        return 1 if tiled else 0
+        return 1 if tiled and k % 8 == 0 and n_out % 2 == 0 else 0
 
     def moe_gate_up(self, h, w_gate_up, routing, out_dtype, tiled=None):
         pair_expert, offsets, order, T, top, experts = routing
@@ -777,7 +798,7 @@ class CudaOps:
         out = torch.empty((T * top, inner), dtype=out_dtype, device=h.device)
         self._call("ember_moe_gate_up", self._dense(h, "rows").data_ptr(), self._dense(w_gate_up, "experts").data_ptr(),
                    pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr(), out.data_ptr(), T, top, experts, width,
-                   inner, self._moe_tiled(T * top, h.dtype, tiled), _code(h.dtype))
+                   inner, self._moe_tiled(T * top, h.dtype, tiled, width, inner), _code(h.dtype))
         return out
 
     def moe_down(self, inner_rows, w_down, routing, tiled=None):
@@ -788,7 +809,7 @@ class CudaOps:
         out = torch.empty((T, top, width), dtype=torch.float32, device=inner_rows.device)
         self._call("ember_moe_down", self._dense(inner_rows, "rows").data_ptr(), self._dense(w_down, "experts").data_ptr(),
                    pair_expert.data_ptr(), offsets.data_ptr(), order.data_ptr(), out.data_ptr(), T, top, experts, width,
-                   inner, self._moe_tiled(T * top, inner_rows.dtype, tiled), _code(inner_rows.dtype))
+                   inner, self._moe_tiled(T * top, inner_rows.dtype, tiled, inner, width), _code(inner_rows.dtype))
         return out
 
     # ------------------------------------------------------------------ sampling

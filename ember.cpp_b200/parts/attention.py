@@ -71,7 +71,7 @@ class CausalAttention(Mixer):
 
     def load(self, get, runtime):
         import torch
-        if runtime.dtype == torch.bfloat16 and ((self.head_dim % 16 and not self.extended) or self.width % 8):
+        if runtime.dtype == torch.bfloat16 and not self.extended and (self.head_dim % 16 or self.width % 8):
             # (the true 32-bit path takes every head size up to 256 and every width)
             raise ValueError(f"attention {self.prefix!r}: the bfloat16 kernels take head sizes that are multiples of 16 "
                              f"and widths that are multiples of 8 (here {self.head_dim} and {self.width}); "

@@ -92,9 +92,6 @@ class GatedFeedForward(FeedForward):
 
     def load(self, get, runtime):
         import torch
-        if runtime.dtype == torch.bfloat16 and (self.inner % 8 or self.width % 8):
-            raise ValueError(f"feed-forward {self.prefix!r}: the bfloat16 kernels take widths that are multiples of 8 "
-                             f"(here width {self.width}, inner {self.inner}); the float32 path takes this model")
         self.w_gate_up = torch.cat([runtime.matrix(get(self.gate_name)), runtime.matrix(get(self.up_name))]).contiguous()
         self.w_down = runtime.matrix(get(self.down_name))
 

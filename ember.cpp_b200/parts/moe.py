@@ -46,9 +46,6 @@ class TableExperts(FeedForward):
 
     def load(self, get, runtime):
         import torch
-        if runtime.dtype == torch.bfloat16 and (self.inner % 8 or self.width % 8):
-            raise ValueError(f"experts {self.prefix!r}: the bfloat16 kernels take widths that are multiples of 8 "
-                             f"(here width {self.width}, inner {self.inner}); the float32 path takes this model")
         table = get(self.table_name).to(torch.int64)
         if int(table.min()) < 0 or int(table.max()) >= self.experts:
             raise ValueError(f"experts {self.prefix!r}: the table names an expert outside [0, {self.experts})")

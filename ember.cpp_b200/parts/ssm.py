@@ -59,9 +59,6 @@ class Mamba2(Mixer):
 
     def load(self, get, runtime):
         import torch
-        if runtime.dtype == torch.bfloat16 and (self.width % 8 or self.inner % 8):
-            raise ValueError(f"mamba2 {self.prefix!r}: the bfloat16 products take widths that are multiples of 8 (here "
-                             f"{self.width} and {self.inner}); the float32 path takes this model")
         n = self.names
         w = runtime.matrix(get(n["proj"]))
         # rows of zeros up to a multiple of 8: every row of the projection's output then starts on 16 bytes

@@ -1,6 +1,7 @@
 """Small Nipolorn configurations and helpers shared by the CPU and GPU tests.
 
-The two configurations differ from one another in every size and option: attention with values
+The first two configurations differ from one another in every size and option (a third has sizes that are no
+multiples of 8 anywhere): attention with values
 wider than keys and grouped heads / plain heads with equal sizes; a window shorter than a page
 with kept first tokens / a window longer than a page with none; Mamba-2 with groups, four taps and
 split norm / one group, two taps, one norm part and sizes that are no powers of two; a clamped
@@ -35,7 +36,14 @@ CONFIGS = {
         _layer(LEFT_B, RIGHT_B, {"kind": "dense", "ff": 160, "limit": 2.5}, 0.8, 1.0),
     ]},
 }
-SEEDS = {"nip_a": 3, "nip_b": 4}
+# sizes that are no multiples of 8 anywhere: rows that are no whole 16-byte pieces in bfloat16
+LEFT_C = {"dim": 12, "vdim": 10, "heads": 3, "kv_heads": 1, "scale": 0.25, "mask": {"size": 9, "keep_first": 2}}
+RIGHT_C = {"heads": 3, "vdim": 6, "groups": 1, "state": 7, "conv": 3, "norm_groups": 3}
+CONFIGS["nip_c"] = {"architecture": "Nipolorn", "vocab": 101, "width": 60, "norm": {"eps": 1e-5}, "layers": [
+    _layer(LEFT_C, RIGHT_C, {"kind": "dense", "ff": 50, "limit": 1.5}, 0.9, 0.7),
+    _layer(LEFT_C, RIGHT_C, {"kind": "moe", "expert": {"ff": 20}, "router": {"experts": 3, "top": 2}, "shared": {"ff": 10}}, 0.6, 1.2),
+]}
+SEEDS = {"nip_a": 3, "nip_b": 4, "nip_c": 5}
 
 
 def config(name: str) -> dict:

@@ -57,13 +57,13 @@ def test_a_bad_value_is_refused_by_its_key(path, value, word):
         config_from_dict(d)
 
 
-def test_bfloat16_refuses_rows_that_are_not_multiples_of_16_bytes_by_key():
+def test_no_size_is_refused_in_either_compute_type():
     d = U.config("nip_b")
     d["layers"][1]["mlp"]["ff"] = 100
+    d["width"] = 60
     cfg = config_from_dict(d)
     cfg.check_dtype("float32")
-    with pytest.raises(ConfigError, match=r"layers\[1\]\.mlp\.ff"):
-        cfg.check_dtype("bfloat16")
+    cfg.check_dtype("bfloat16")
 
 
 def test_the_spec_follows_the_configuration():
@@ -145,7 +145,7 @@ def test_plain_recurrence_does_not_depend_on_where_a_sequence_is_cut(plains):
 
 
 # ------------------------------------------------------------------------------ the step function over the CPU double
-@pytest.mark.parametrize("name", ["nip_a", "nip_b"])
+@pytest.mark.parametrize("name", ["nip_a", "nip_b", "nip_c"])
 def test_steps_equal_whole_sequences(folders, plains, name):
     """Whole prompts, one token at a time from the first token on, portions down to two tokens, and unequal
     batches decoded together: all give the plain implementation's logits at every position."""

@@ -332,6 +332,19 @@ def test_prompts_decoding_portions_and_batches_equal_the_plain_model(engines, pl
     assert eng.cache.slots.held == 0 and all(g.pages.held == 0 for g in eng.cache.groups)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_are_no_multiples_of_8_run_in_both_compute_types(engines, plains, dtype):
+    """Width 60, heads of 12 with values of 10, 7 states, inner sizes 50, 20 and 10: in bfloat16 the products whose
+    rows are no whole 16-byte pieces take the float32 product on the same values, everything else its scalar form."""
+    eng, m = engines[("nip_c", dtype)], plains["nip_c"]
+    seqs = [U.ids(90 + i, 101, n) for i, n in enumerate((140, 3, 66))]
+    refs = [P.forward(m, s) for s in seqs]
+    for prompts in ([len(s) for s in seqs], [100, 1, 2]):
+        got, _ = run_batch(eng, seqs, prompts)
+        assert max(U.row_error(g, r) for g, r in zip(got, refs)) < U.TOL[dtype]
+    eng.ops.check()
+
+
 def test_in_32_bit_a_row_does_not_depend_on_the_batch_or_the_cut(engines):
     """Every sum of the 32-bit path is made in an order that the row's own sequence fixes."""
     eng = engines[("nip_a", "float32")]
