@@ -219,6 +219,9 @@ class CudaOps:
         #   kernel and the split one-token kernel where they have the sizes; False takes the plain kernel everywhere
         #   (a measurement switch: the twin that the two are compared with)
         self.attention_kept_fast = True
+        # branch_streams: `side_by_side` runs independent branches of a one-token step on streams of their own
+        self.branch_streams = options.branch_streams
+        self._side_streams = []
         # op_timing, nvtx: per-launch CUDA events and NVTX ranges (see options.py); both off by default
         self.op_timing, self.nvtx = options.op_timing, options.nvtx
         self._timed = []
@@ -658,6 +661,34 @@ class CudaOps:
                    plan.max_blocks, plan.T, n_heads, kv_heads, hd, float(scale), int(window), vd, keep_first,
                    _code(qkv.dtype))
         return out
+
+    # ------------------------------------------------------------------ branches side by side
+    def side_by_side(self, branches):
+        """Runs independent pieces of a step (callables that launch kernels and return their results) and returns
+        their results in order.  With `branch_streams` the first runs on the current stream and every other one on a
+        stream of its own that waits for what the current stream has queued so far; the current stream then waits
+        for all of them.  Inside a captured graph the branches become parallel paths of the graph.  A branch must
+        read only what was queued before the call and write only what the others do not touch."""
+        if not self.branch_streams or len(branches) < 2:
+            return [run() for run in branches]
+        while len(self._side_streams) < len(branches) - 1:
+            self._side_streams.append(torch.cuda.Stream())
+        main = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(main)
+        results, joins = [None] * len(branches), []
+        for k, run in enumerate(branches[1:], 1):
+            side = self._side_streams[k - 1]
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                results[k] = run()
+                done = torch.cuda.Event()
+                done.record(side)
+            joins.append(done)
+        results[0] = branches[0]()
+        for done in joins:
+            main.wait_event(done)
+        return results
 
     # ------------------------------------------------------------------ RMS norm, gates
     def rmsnorm(self, x, w, eps, out_dtype, offset=0.0):

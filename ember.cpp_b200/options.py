@@ -28,6 +28,8 @@ options given in code), so a measurement can flip a switch without touching the 
   cache_ahead      EMBER_CACHE_AHEAD      a decode attention asks the next layer's rows of the cache into L2
   warm             EMBER_WARM             a product asks into L2 the weights that a part announced for the product after it
                                           (a feed-forward its second matrix; the tcgen05 streaming product the next matrix)
+  branch_streams   EMBER_BRANCH_STREAMS   in a one-token step, mixers that stand side by side on the same input (and a shared expert beside
+                                          the chosen ones) run on streams of their own, forked from and joined to the step's stream
   op_timing        EMBER_OP_TIMING        every launch is bracketed by CUDA events; `CudaOps.op_times()` gives the time per
                                           kernel entry point (ember.cpp: EMBER_OP_TIMING=1, model.h:465-467).  Steps then run
                                           launch by launch (no graph) and without overlap between kernels: read the shares
@@ -74,6 +76,7 @@ class RuntimeOptions:
     pdl: bool = True
     cache_ahead: bool = False
     warm: bool = True
+    branch_streams: bool = True
     op_timing: bool = False
     nvtx: bool = False
 

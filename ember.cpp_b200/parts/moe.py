@@ -58,15 +58,20 @@ class TableExperts(FeedForward):
     def stream_weights(self):
         return self.shared.stream_weights() if self.shared is not None else []
 
-    def branches(self, ctx, h):
+    def _chosen(self, ctx, h):
         ops = ctx.ops
         routing = ops.moe_route(ctx.plan.tokens, ctx.plan.T, self.table, self.experts, self.top)
         inner = ops.moe_gate_up(h, self.w_gate_up, routing, out_dtype=ctx.dtype)     # [T * top, inner], silu(g) * u
         y = ops.moe_down(inner, self.w_down, routing)                                 # float32 [T, top, width]
-        out = [(y[:, k, :], 1.0 / self.top) for k in range(self.top)]
-        if self.shared is not None:
-            out += self.shared.branches(ctx, h)
-        return out
+        return [(y[:, k, :], 1.0 / self.top) for k in range(self.top)]
+
+    def branches(self, ctx, h):
+        if self.shared is None:
+            return self._chosen(ctx, h)
+        runs = [lambda: self._chosen(ctx, h), lambda: self.shared.branches(ctx, h)]
+        together = getattr(ctx.ops, "side_by_side", None)     # (one-token steps: the shared expert beside the chosen ones)
+        chosen, shared = together(runs) if together is not None and ctx.plan.all_single else [run() for run in runs]
+        return chosen + shared
 
     def forward(self, ctx, h, residual):
         x = residual

@@ -70,9 +70,14 @@ class ParallelMixers(Mixer):
         return dataclasses.replace(app, state=state)
 
     def branches(self, ctx, h, app):
+        runs = [lambda name=name, m=m: m.branches(ctx, h, self._handle(app, name, m)) for name, m, _ in self.members]
+        # in a one-token step the members' chains of small kernels can run beside one another (they share their
+        # input and nothing else: the cache is one member's, the states are kept apart)
+        together = getattr(ctx.ops, "side_by_side", None)
+        results = together(runs) if together is not None and ctx.plan.all_single else [run() for run in runs]
         out = []
-        for name, m, factor in self.members:
-            out += [(rows, f * factor) for rows, f in m.branches(ctx, h, self._handle(app, name, m))]
+        for (_, _, factor), rows in zip(self.members, results):
+            out += [(r, f * factor) for r, f in rows]
         return out
 
     def forward(self, ctx, h, residual, app):
