@@ -72,6 +72,67 @@ __global__ void conv_silu_kernel(const T* __restrict__ in, long long in_stride, 
   }
 }
 
+// The same with two neighbouring channels a thread (4- or 8-byte loads and stores: half the instructions for the
+// same bytes), where the number of channels, the first column and the row stride are even.
+__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 load2(const __nv_bfloat16* p) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+__device__ __forceinline__ void store2(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+__device__ __forceinline__ void store2(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+template <typename T, int TMAX>
+__global__ void conv_silu2_kernel(const T* __restrict__ in, long long in_stride, int col0, int channels, int taps,
+                                  const float* __restrict__ w, const float* __restrict__ bias,
+                                  const float* __restrict__ state, T* __restrict__ out, const int* __restrict__ seq_slot,
+                                  const int* __restrict__ seq_start, const int* __restrict__ cu_new, int runs) {
+  const int c = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
+  if (c >= channels) return;
+  const int s = blockIdx.x / runs, run = blockIdx.x % runs;
+  const int t0 = cu_new[s], n = cu_new[s + 1] - t0;
+  const int i0 = run * kConvRun, i1 = min(n, i0 + kConvRun);
+  if (i0 >= n) return;
+  const int slot = seq_slot[s];
+  if (slot < 0) {
+    for (int i = i0; i < i1; ++i) store2(out + (size_t)(t0 + i) * channels + c, 0.f, 0.f);
+    return;
+  }
+  const bool carried = seq_start[s] > 0;
+  const float* st = state + (size_t)slot * (taps - 1) * channels + c;
+  const T* src = in + (size_t)t0 * in_stride + col0 + c;
+  float2 hist[TMAX], wt[TMAX];
+#pragma unroll
+  for (int m = 0; m < TMAX; ++m) {
+    wt[TMAX - 1 - m] = m < taps ? make_float2(w[(size_t)c * taps + taps - 1 - m], w[(size_t)(c + 1) * taps + taps - 1 - m])
+                                : make_float2(0.f, 0.f);
+    float2 v = make_float2(0.f, 0.f);
+    if (m >= 1 && m < taps) {
+      const int at = i0 - m;
+      if (at >= 0)
+        v = load2(src + (size_t)at * in_stride);
+      else if (carried)
+        v = load2(st + (size_t)(taps - 1 + at) * channels);
+    }
+    hist[TMAX - 1 - m] = v;
+  }
+  const float2 b = load2(bias + c);
+#pragma unroll 8
+  for (int i = i0; i < i1; ++i) {
+    hist[TMAX - 1] = load2(src + (size_t)i * in_stride);
+    float a0 = b.x, a1 = b.y;
+#pragma unroll
+    for (int k = 0; k < TMAX; ++k) {
+      a0 = fmaf(wt[k].x, hist[k].x, a0);
+      a1 = fmaf(wt[k].y, hist[k].y, a1);
+    }
+    store2(out + (size_t)(t0 + i) * channels + c, silu_f(a0), silu_f(a1));
+#pragma unroll
+    for (int k = 0; k + 1 < TMAX; ++k) hist[k] = hist[k + 1];
+  }
+}
+
 // The state after the step: its row k is the input taps - 1 - k rows before the sequence's new end.
 // One thread per (sequence, channel), rows in ascending order (row k is read from a later row only).
 template <typename T>
@@ -744,12 +805,18 @@ EMBER_API int ember_conv_silu(const void* in, long long in_stride, int col0, int
   EMBER_CHECK(max_new >= 1, "conv_silu: the longest sequence brings %d tokens", max_new);
   const int bx = (channels + 127) / 128;
   const int runs = (max_new + kConvRun - 1) / kConvRun;  // of the longest sequence
+  const int elem = dtype == EMBER_F32 ? 4 : 2;
+  const bool pairs = channels % 2 == 0 && col0 % 2 == 0 && in_stride % 2 == 0 && (uintptr_t)in % (2 * elem) == 0 &&
+                     (uintptr_t)out % (2 * elem) == 0 && (uintptr_t)bias % 8 == 0 && (taps == 1 || (uintptr_t)state % 8 == 0);
   EMBER_CHECK(bx <= 65535, "conv_silu: %d channels exceed one launch", channels);
 #define EMBER_CONV(TT)                                                                                                    \
   do {                                                                                                                    \
     if (all_single && T == n_seqs) {                                                                                      \
       launch_plain(conv_step_kernel<TT>, dim3(T, bx), dim3(128), 0, stream, (const TT*)in, in_stride, col0, channels, taps, \
                  w, bias, state, (TT*)out, seq_slot, seq_start);                                                          \
+    } else if (taps <= 4 && pairs) {                                                                                      \
+      conv_silu2_kernel<TT, 4><<<dim3(n_seqs * runs, (channels / 2 + 127) / 128), 128, 0, stream>>>(                      \
+          (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs);   \
     } else if (taps <= 4) {                                                                                               \
       conv_silu_kernel<TT, 4><<<dim3(n_seqs * runs, bx), 128, 0, stream>>>(                                               \
           (const TT*)in, in_stride, col0, channels, taps, w, bias, state, (TT*)out, seq_slot, seq_start, cu_new, runs);   \
