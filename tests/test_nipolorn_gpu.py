@@ -243,7 +243,7 @@ def plain_attention_rows(qkv, heads, kv, hd, vd, window, keep, scale):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, kv, hd, vd, window, keep", [(4, 2, 80, 80, 70, 5), (6, 3, 24, 40, 33, 66), (2, 1, 64, 64, 130, 0),
-                                                            (4, 4, 32, 32, 64, 64), (2, 2, 16, 16, 1, 1), (2, 1, 16, 20, 33, 2)])
+                                                            (4, 4, 32, 32, 64, 64), (2, 2, 16, 16, 1, 1), (2, 1, 16, 20, 33, 2), (6, 2, 32, 32, 40, 3), (10, 2, 16, 16, 100, 0)])
 def test_attention_with_window_and_kept_first_tokens(ops, dtype, heads, kv, hd, vd, window, keep):
     """Prompts of unequal length, portions on top of a cache, one token each; windows shorter and longer than a
     page, kept tokens within one page and across two; values wider than keys."""
