@@ -123,7 +123,8 @@ class CacheView:
 
 class SequenceCache:
     def __init__(self, needs: list[tuple[CacheNeed | None, StateNeed | None]], cache_of: list[int | None],
-                 max_tokens: int, max_positions: int | None, dtype, device, max_slots: int | None = None):
+                 max_tokens: int, max_positions: int | None, dtype, device, max_slots: int | None = None,
+                 model_states: dict | None = None):
         if max_tokens <= 0:
             raise CacheError(f"max_tokens = {max_tokens} must be positive")
         self.n_pages = -(-int(max_tokens) // PAGE)
@@ -162,6 +163,9 @@ class SequenceCache:
         # per application: None, one tensor [slots, *shape], or (a mixer with several) a dict of them by name
         self.states = [None if s is None else ({k: make(v) for k, v in s.items()} if isinstance(s, dict) else make(s))
                        for s in self.state_needs]
+        # state that belongs to the model and to no layer (what its embedding carries), by name
+        self.model_state_needs = dict(model_states or {})
+        self.model_states = {name: make(need) for name, need in self.model_state_needs.items()}
 
     # ------------------------------------------------------------------ slots
     def open(self) -> int:
@@ -176,6 +180,8 @@ class SequenceCache:
                     t[slot].fill_(need[name].init)
             elif state is not None:
                 state[slot].fill_(need.init)
+        for name, t in self.model_states.items():
+            t[slot].fill_(self.model_state_needs[name].init)
         return slot
 
     def close(self, slot: int) -> None:
@@ -198,6 +204,7 @@ class SequenceCache:
                 yield from state.values()
             elif state is not None:
                 yield state
+        yield from self.model_states.values()
 
     def save_states(self, slots) -> list:
         """Copies of the state rows of `slots` in every state tensor (for `restore_states`).  A step that
@@ -274,7 +281,7 @@ class SequenceCache:
         cur = self.length(slot)
         if not 0 <= length <= cur:
             raise CacheError(f"slot {slot}: cannot truncate {cur} positions to {length}")
-        if any(s is not None for s in self.states) and length != cur:
+        if (any(s is not None for s in self.states) or self.model_states) and length != cur:
             raise CacheError("a layer keeps per-sequence state; truncation would need a snapshot")
         for g in self.groups:
             first = g.first_needed_block(length)

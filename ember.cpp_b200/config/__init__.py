@@ -2,7 +2,8 @@
 from .base import (Architecture, ConfigError, ModelConfig, architectures, config_from_dict, get_architecture,
                    load_config, register_architecture)
 from .gpt2 import GELU_FORMS, GPT2Config
+from .muzozen import MuzozenConfig
 from .nipolorn import NipolornConfig
 
-__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "NipolornConfig", "architectures",
+__all__ = ["Architecture", "ConfigError", "GELU_FORMS", "GPT2Config", "ModelConfig", "MuzozenConfig", "NipolornConfig", "architectures",
            "config_from_dict", "get_architecture", "load_config", "register_architecture"]

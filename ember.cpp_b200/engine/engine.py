@@ -80,6 +80,7 @@ class StepContext:
     apps: list
     position: object
     next_weights: tuple = ()   # set by the model: the first matrix that the block after the current one streams
+    model_state: dict = dataclasses.field(default_factory=dict)   # per-sequence state of the parts in front of the layers
 
 
 class Engine:
@@ -92,7 +93,8 @@ class Engine:
         spec = model.spec
         self.vocab_size = spec.vocab_size
         self.cache = SequenceCache(model.application_needs(), [a.cache_of for a in spec.schedule], max_tokens,
-                                   model.max_positions(), runtime.dtype, runtime.device, max_slots)
+                                   model.max_positions(), runtime.dtype, runtime.device, max_slots,
+                                   model.model_state_needs())
         self.apps = [AppHandle(i, a.layer, self.cache.views[i], self.cache.writes[i], self.cache.states[i])
                      for i, a in enumerate(spec.schedule)]
         self._device_buffer = None
@@ -273,7 +275,8 @@ class Engine:
         self.counters["decode_tokens" if host.all_single else "prompt_tokens"] += sum(n for _, n in shape)
 
     def run(self, plan: StepPlan):
-        ctx = StepContext(self.ops, self.runtime.dtype, plan, self.apps, self.model.position)
+        ctx = StepContext(self.ops, self.runtime.dtype, plan, self.apps, self.model.position,
+                          model_state=self.cache.model_states)
         if getattr(self.ops, "nvtx", False):
             torch.cuda.nvtx.range_push(f"step {'decode' if plan.all_single else 'prefill'} T={plan.T} n={plan.n}")
             try:

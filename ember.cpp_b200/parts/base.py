@@ -12,6 +12,8 @@ Roles and what each must provide:
             (mixer and ffn also: branches(ctx, h[, app]) -> [(float32 rows, factor)], the output as a weighted
             sum that the caller adds itself, for arrangements that norm a sublayer's output before the sum;
             a norm's add_normed(ctx, x, branches) makes that sum, norms it and adds it to the stream)
+  embed     forward(ctx, x, state) -> x     (adds to the embedded rows; state_need() as a mixer's: what it
+            carries per sequence, kept by the cache beside the layers' states)
   position  embedding_table() -> tensor | None, max_positions() -> int | None,
             apply_qk(ctx, qkv, n_heads, kv_heads, head_dim) (in place; default: nothing)
   block     forward(ctx, x, app) -> x       (the arrangement of the four parts above)
@@ -141,6 +143,19 @@ class FeedForward(Part):
         return [(self.forward(ctx, h, zero), 1.0)]
 
 
+class EmbedPart(Part):
+    """Something added to the embedded rows before the first layer (rows of a second table chosen by more
+    than the token itself).  It reads the step's tokens (`ctx.plan.tokens`)."""
+    role = "embed"
+    needs_tokens = True
+
+    def state_need(self) -> "StateNeed | dict[str, StateNeed] | None":
+        return None
+
+    def forward(self, ctx, x, state):
+        raise NotImplementedError
+
+
 class Position(Part):
     role = "position"
 
@@ -169,7 +184,7 @@ class Block(Part):
         raise NotImplementedError
 
 
-_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", "mixer", "ffn", "position", "block")}
+_REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {r: {} for r in ("norm", "mixer", "ffn", "position", "block", "embed")}
 
 
 def register_part(role: str, kind: str, factory: Callable[..., Part]) -> None:

@@ -10,6 +10,10 @@ their last projection can do the sum in its epilogue.
 here (it is normed first), so the sublayer hands over its output as a weighted sum of float32
 rows (`branches`) and the norm after it sums, norms and adds in one launch.  A layer of this
 arrangement may have no feed-forward; it then has no norms around one either.
+
+`shared_norm` has one norm that both sublayers read: `h = norm1(x)`, `x -> x + mixer(h) + ffn(h)`.
+The mixer's last projection adds into the stream and the feed-forward's adds into that, both in
+float32; a layer of this arrangement may have no feed-forward.
 """
 from __future__ import annotations
 
@@ -58,5 +62,22 @@ class SandwichBlock(Block):
         return self.more_norms["after_ffn"].add_normed(ctx, x, self.ffn.branches(ctx, h))
 
 
+class SharedNormBlock(Block):
+    def __init__(self, norm1, mixer, norm2, ffn, **more_norms):
+        if norm1 is None or norm2 is not None or more_norms:
+            raise ValueError("block 'shared_norm' has exactly one norm, which the mixer and the feed-forward both read")
+        super().__init__(norm1, mixer, None, ffn)
+
+    def forward(self, ctx, x, app):
+        announce = getattr(ctx.ops, "announce_weights", None)
+        if announce is not None:
+            announce(self.mixer.stream_weights() + (self.ffn.stream_weights() if self.ffn is not None else [])
+                     + list(getattr(ctx, "next_weights", ())))
+        h = self.norm1.forward(ctx, x, ctx.dtype)
+        x = self.mixer.forward(ctx, h, x, app)
+        return x if self.ffn is None else self.ffn.forward(ctx, h, x)
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "shared_norm", SharedNormBlock)
 register_part("block", "sandwich", SandwichBlock)

@@ -21,8 +21,10 @@ class DenseFeedForward(FeedForward):
 
     def __init__(self, prefix: str, width: int, inner: int, activation: str, up: str = "c_fc", down: str = "c_proj",
                  stored: str = "in_out", bias: bool = True, init_std: float = 0.02, down_init_std: float = 0.02,
-                 bias_init_std: float = 0.01):
+                 bias_init_std: float = 0.01, suffix: str = ".weight", any_size: bool = False):
         super().__init__(prefix)
+        self.any_size = any_size  # True: widths that are no multiples of 8 are left to the slower products in bfloat16
+        self.suffix = suffix      # what follows a matrix's name in the checkpoint ("" for names without one)
         if activation not in ACTIVATIONS:
             raise ValueError(f"feed-forward {prefix!r}: activation {activation!r} is not one of {ACTIVATIONS}")
         if stored not in ("in_out", "out_in"):
@@ -36,8 +38,8 @@ class DenseFeedForward(FeedForward):
         return (n_in, n_out) if self.stored == "in_out" else (n_out, n_in)
 
     def weight_specs(self):
-        specs = [WeightSpec(self.up_name + ".weight", self._shape(self.width, self.inner), std=self.init_std),
-                 WeightSpec(self.down_name + ".weight", self._shape(self.inner, self.width), std=self.down_init_std)]
+        specs = [WeightSpec(self.up_name + self.suffix, self._shape(self.width, self.inner), std=self.init_std),
+                 WeightSpec(self.down_name + self.suffix, self._shape(self.inner, self.width), std=self.down_init_std)]
         if self.bias:
             specs += [WeightSpec(self.up_name + ".bias", (self.inner,), std=self.bias_init_std),
                       WeightSpec(self.down_name + ".bias", (self.width,), std=self.bias_init_std)]
@@ -45,12 +47,12 @@ class DenseFeedForward(FeedForward):
 
     def load(self, get, runtime):
         import torch
-        if runtime.dtype == torch.bfloat16 and (self.inner % 8 or self.width % 8):
+        if runtime.dtype == torch.bfloat16 and (self.inner % 8 or self.width % 8) and not self.any_size:
             raise ValueError(f"feed-forward {self.prefix!r}: the bfloat16 kernels take widths that are multiples of 8 "
                              f"(rows of 16 bytes; here width {self.width}, inner {self.inner}); the float32 path takes this model")
         t = self.stored == "in_out"
-        self.w_up = runtime.matrix(get(self.up_name + ".weight"), transpose=t)
-        self.w_down = runtime.matrix(get(self.down_name + ".weight"), transpose=t)
+        self.w_up = runtime.matrix(get(self.up_name + self.suffix), transpose=t)
+        self.w_down = runtime.matrix(get(self.down_name + self.suffix), transpose=t)
         if self.bias:
             self.b_up = runtime.vector(get(self.up_name + ".bias"))
             self.b_down = runtime.vector(get(self.down_name + ".bias"))

@@ -27,6 +27,8 @@ class DecoderModel:
             self.blocks.append(build_block(layer.block, norm(layer.norm1), build_part("mixer", layer.mixer), norm(layer.norm2),
                                            None if layer.ffn is None else build_part("ffn", layer.ffn), {name: norm(part) for name, part in layer.more_norms}))
         self.final_norm = build_part("norm", spec.final_norm)
+        self.embed_parts = [build_part("embed", part) for part in spec.embed_parts]
+        self.embed_norm = None if spec.embed_norm is None else build_part("norm", spec.embed_norm)
         self.table = None
         self.head = None
         self.head_bias = None
@@ -34,7 +36,7 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ tensors
     def all_parts(self):
-        parts = [self.position]
+        parts = [self.position] + self.embed_parts + ([] if self.embed_norm is None else [self.embed_norm])
         for b in self.blocks:
             parts += b.parts()
         return parts + [self.final_norm]
@@ -78,6 +80,25 @@ class DecoderModel:
             out.append((need, mixer.state_need()))
         return out
 
+    def model_state_needs(self) -> dict:
+        """Per-sequence state that belongs to no layer: what the parts in front of the first layer carry,
+        by the part's place among them (and the state's name where a part keeps several)."""
+        need = {}
+        for i, part in enumerate(self.embed_parts):
+            s = part.state_need()
+            if s is None:
+                continue
+            for key, one in (s.items() if isinstance(s, dict) else [("", s)]):
+                need[f"embed{i}.{key}"] = one
+        return need
+
+    def _embed_state(self, ctx, i, part):
+        s = part.state_need()
+        if s is None:
+            return None
+        states = ctx.model_state
+        return {key: states[f"embed{i}.{key}"] for key in s} if isinstance(s, dict) else states[f"embed{i}."]
+
     # ------------------------------------------------------------------ one step
     def forward(self, ctx):
         """Runs the tokens of `ctx.plan` through every entry of the schedule and returns float32
@@ -95,6 +116,10 @@ class DecoderModel:
             x = ops.embed(plan.tokens, plan.positions, self.table, self.position.embedding_table())
         if self.spec.embedding_scale != 1.0:
             x = ops.scale_cap(x, scale=self.spec.embedding_scale)
+        for i, part in enumerate(self.embed_parts):
+            x = part.forward(ctx, x, self._embed_state(ctx, i, part))
+        if self.embed_norm is not None:
+            x = self.embed_norm.forward(ctx, x, torch.float32)
         for i, app in enumerate(ctx.apps):
             # (a hint for the kernels: the first matrix that the block after this one streams)
             following = ctx.apps[i + 1].layer if i + 1 < len(ctx.apps) else None

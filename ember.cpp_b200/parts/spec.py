@@ -67,6 +67,10 @@ class ModelSpec:
     # prefixes that a checkpoint's tensor names may carry in front of the names the parts use (a
     # wrapper module's name); a detail of the architecture's checkpoints, so it stands here
     strip_prefixes: tuple[str, ...] = ()
+    # parts of the `embed` role that add to the embedded rows (after `embedding_scale`), in order, and a norm of the
+    # sum: what stands between the token table and the first layer in a model that has more there than a table
+    embed_parts: tuple[PartSpec, ...] = ()
+    embed_norm: PartSpec | None = None
 
     def check(self) -> None:
         if not self.layers:

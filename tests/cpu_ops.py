@@ -157,12 +157,108 @@ class CpuOps:
             state[slot] = S
         return y
 
-    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype):
+    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype, gate_first=True):
         n = y.shape[1]
         z = proj[:, z_col:z_col + n].float()
-        g = (y * z * torch.sigmoid(z)).view(y.shape[0], parts, n // parts)
-        g = g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)
-        return (g.reshape(y.shape[0], n) * w).to(out_dtype)
+        gate = z * torch.sigmoid(z)
+        g = (y * gate if gate_first else y).view(y.shape[0], parts, n // parts)
+        g = (g * torch.rsqrt((g * g).mean(-1, keepdim=True) + eps)).reshape(y.shape[0], n) * w
+        return (g if gate_first else g * gate).to(out_dtype)
+
+    # ------------------------------------------------------------------ a table of token pairs
+    def pair_table_add(self, x, plan, table, state, mul_prev, mul_cur, buckets):
+        tokens = plan.tokens.tolist()
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            for t in range(t0, t1):
+                if start + t - t0 == 0:
+                    row = buckets
+                else:
+                    prev = tokens[t - 1] if t > t0 else int(state[slot, 0])
+                    row = (prev * mul_prev + tokens[t] * mul_cur) % buckets
+                x[t] += table[row].float()
+            state[slot, 0] = tokens[t1 - 1]
+        return x
+
+    # ------------------------------------------------------------------ rotation, rows of low rank, products per head
+    def rotate(self, src, dst, positions, heads, src_col, src_head, dst_col, dst_head, width, freqs, magnitude, dims):
+        half = dims // 2
+        a = positions.double()[:, None] * freqs.double()[None, :]
+        c, s = (torch.cos(a) * magnitude).float(), (torch.sin(a) * magnitude).float()
+        for h in range(heads):
+            x = src[:, src_col + h * src_head: src_col + h * src_head + width].float()
+            u, v = x[:, :half], x[:, half:dims]
+            y = torch.cat([u * c - v * s, v * c + u * s, x[:, dims:]], 1)
+            dst[:, dst_col + h * dst_head: dst_col + h * dst_head + width] = y.to(dst.dtype)
+        return dst
+
+    def latent_rows(self, down, plan, q_rank, q_norm, kv_norm, kv_rank, rot_dim, eps, rotary, cache, out_dtype):
+        c_q = self.rmsnorm(down[:, :q_rank], q_norm, eps, out_dtype)
+        if cache is not None:
+            c = self.rmsnorm(down[:, q_rank:q_rank + kv_rank], kv_norm, eps, torch.float32)
+            k_r = torch.zeros(down.shape[0], rot_dim)
+            self.rotate(down, k_r, plan.positions, 1, q_rank + kv_rank, rot_dim, 0, rot_dim, rot_dim, rotary.freqs,
+                        rotary.magnitude, rotary.dims)
+            g = cache.group_index
+            for t in range(plan.T):
+                s = int(plan.token_seq[t])
+                if int(plan.seq_slot[s]) < 0:
+                    continue
+                p = int(plan.positions[t])
+                page = int(plan.pages[g][s, p // PAGE])
+                assert page >= 0, "a position is written whose page is not held"
+                cache.k[page, 0, p % PAGE, :] = c[t].to(cache.k.dtype)
+                cache.v[page, 0, p % PAGE, :] = k_r[t].to(cache.v.dtype)
+        return c_q
+
+    def head_linear(self, a, a_col, a_head, w, out, out_col, out_head):
+        heads, n, k = w.shape
+        for h in range(heads):
+            out[:, out_col + h * out_head: out_col + h * out_head + n] = \
+                (a[:, a_col + h * a_head: a_col + h * a_head + k].float() @ w[h].float().t()).to(out.dtype)
+        return out
+
+    def latent_attention(self, rows, cache, plan, heads, kv_rank, rot_dim, scale, out_dtype):
+        g = cache.group_index
+        out = torch.zeros(plan.T, heads * kv_rank)
+        q = rows.float().view(plan.T, heads, kv_rank + rot_dim)
+        for t in range(plan.T):
+            s = int(plan.token_seq[t])
+            if int(plan.seq_slot[s]) < 0:
+                continue
+            pos = torch.arange(0, int(plan.positions[t]) + 1)
+            pages = plan.pages[g][s, pos // PAGE].long()
+            assert (pages >= 0).all(), "a position is read whose page is not held"
+            c = cache.k[pages, 0, pos % PAGE, :].float()
+            k_r = cache.v[pages, 0, pos % PAGE, :].float()
+            sc = (q[t, :, :kv_rank] @ c.t() + q[t, :, kv_rank:] @ k_r.t()) * scale          # [heads, keys]
+            out[t] = (torch.softmax(sc, 1) @ c).reshape(-1)
+        return out.to(out_dtype)
+
+    # ------------------------------------------------------------------ gated delta rule
+    def delta_rule(self, qkv, proj, b_col, a_col, a_log, dt_bias, state, plan, heads, kv_heads, dim, vdim, unit_eps):
+        qk = kv_heads * dim
+        out = torch.zeros(qkv.shape[0], heads * vdim)
+        per = heads // kv_heads
+        for slot, start, t0, t1 in self._sequences(plan):
+            if slot < 0:
+                continue
+            S = state[slot].clone() if start > 0 else torch.zeros(heads, dim, vdim)
+            for t in range(t0, t1):
+                q = qkv[t, :qk].float().view(kv_heads, dim)
+                k = qkv[t, qk:2 * qk].float().view(kv_heads, dim)
+                q = (q * torch.rsqrt((q * q).sum(-1, keepdim=True) + unit_eps) * dim ** -0.5).repeat_interleave(per, 0)
+                k = (k * torch.rsqrt((k * k).sum(-1, keepdim=True) + unit_eps)).repeat_interleave(per, 0)
+                v = qkv[t, 2 * qk:].float().view(heads, vdim)
+                beta = torch.sigmoid(proj[t, b_col:b_col + heads].float())
+                g = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(proj[t, a_col:a_col + heads].float() + dt_bias))
+                S = g[:, None, None] * S
+                u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", S, k))
+                S = S + k[:, :, None] * u[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", S, q).reshape(-1)
+            state[slot] = S
+        return out
 
     # ------------------------------------------------------------------ experts by table
     def moe_route(self, tokens, T, table, experts, top):
