@@ -161,7 +161,8 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
 // out = unit(y * silu(z)) * w, the root mean square taken over each of `parts` equal pieces of a row.
 // y float32 [T, n]; z: n columns of a wider matrix (row stride z_stride).  grid (T, parts).
 // VEC: the part's width, the row widths and the gate's row stride are multiples of 4 (and the gate's first column too).
-template <typename T, bool VEC>
+// GATE_FIRST false: out = unit(y) * w * silu(z), the root mean square being y's own (the gate comes after the norm).
+template <typename T, bool VEC, bool GATE_FIRST>
 __global__ void __launch_bounds__(kThreads)
 gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, long long z_stride,
                         const float* __restrict__ w, T* __restrict__ out, int n, int part, float eps) {
@@ -175,26 +176,30 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
   if constexpr (VEC) {
     for (int i = threadIdx.x * 4; i < part; i += kThreads * 4) {
       const float4 a = load4(yr + i), g = load4(zr + i);
-      const float v0 = a.x * (g.x * sigmoidf(g.x)), v1 = a.y * (g.y * sigmoidf(g.y)), v2 = a.z * (g.z * sigmoidf(g.z)),
-                  v3 = a.w * (g.w * sigmoidf(g.w));
+      const float v0 = GATE_FIRST ? a.x * (g.x * sigmoidf(g.x)) : a.x, v1 = GATE_FIRST ? a.y * (g.y * sigmoidf(g.y)) : a.y,
+                  v2 = GATE_FIRST ? a.z * (g.z * sigmoidf(g.z)) : a.z, v3 = GATE_FIRST ? a.w * (g.w * sigmoidf(g.w)) : a.w;
       ss = fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, fmaf(v3, v3, ss))));
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
     for (int i = threadIdx.x * 4; i < part; i += kThreads * 4) {
       const float4 a = load4(yr + i), g = load4(zr + i), gain = load4(w + c0 + i);
-      store4(o + i, a.x * (g.x * sigmoidf(g.x)) * inv * gain.x, a.y * (g.y * sigmoidf(g.y)) * inv * gain.y,
-             a.z * (g.z * sigmoidf(g.z)) * inv * gain.z, a.w * (g.w * sigmoidf(g.w)) * inv * gain.w);
+      if constexpr (GATE_FIRST)
+        store4(o + i, a.x * (g.x * sigmoidf(g.x)) * inv * gain.x, a.y * (g.y * sigmoidf(g.y)) * inv * gain.y,
+               a.z * (g.z * sigmoidf(g.z)) * inv * gain.z, a.w * (g.w * sigmoidf(g.w)) * inv * gain.w);
+      else
+        store4(o + i, a.x * inv * gain.x * (g.x * sigmoidf(g.x)), a.y * inv * gain.y * (g.y * sigmoidf(g.y)),
+               a.z * inv * gain.z * (g.z * sigmoidf(g.z)), a.w * inv * gain.w * (g.w * sigmoidf(g.w)));
     }
   } else {
     for (int i = threadIdx.x; i < part; i += kThreads) {
       const float zv = to_float(zr[i]);
-      const float v = yr[i] * (zv * sigmoidf(zv));
+      const float v = GATE_FIRST ? yr[i] * (zv * sigmoidf(zv)) : yr[i];
       ss = fmaf(v, v, ss);
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
     for (int i = threadIdx.x; i < part; i += kThreads) {
       const float zv = to_float(zr[i]);
-      o[i] = from_float<T>(yr[i] * (zv * sigmoidf(zv)) * inv * w[c0 + i]);
+      o[i] = from_float<T>(GATE_FIRST ? yr[i] * (zv * sigmoidf(zv)) * inv * w[c0 + i] : yr[i] * inv * w[c0 + i] * (zv * sigmoidf(zv)));
     }
   }
 }
@@ -262,7 +267,7 @@ EMBER_API int ember_gated_act(const void* gu, void* out, int rows, int n, int ki
 }
 
 EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_stride, const float* w, void* out, int rows,
-                                     int n, int parts, float eps, int dtype, cudaStream_t stream) {
+                                     int n, int parts, float eps, int gate_first, int dtype, cudaStream_t stream) {
   EMBER_CHECK(rows > 0 && n > 0 && parts > 0 && n % parts == 0, "gated_group_norm: %d rows of %d in %d parts", rows, n, parts);
   EMBER_CHECK(parts <= 65535, "gated_group_norm: %d parts exceed one launch", parts);
   const dim3 grid(rows, parts);
@@ -270,9 +275,10 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
   const bool vec = (n / parts) % 4 == 0 && n % 4 == 0 && z_stride % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)w % 16 == 0 &&
                    (uintptr_t)z % (4 * elem) == 0 && (uintptr_t)out % (4 * elem) == 0;
   cudaError_t e;
-#define EMBER_GGN(T, VEC)                                                                                              \
-  launch_plain(gated_group_norm_kernel<T, VEC>, grid, dim3(kThreads), 0, stream, y, (const T*)z, z_stride, w, (T*)out, n, \
-               n / parts, eps)
+#define EMBER_GGN1(T, VEC, FIRST)                                                                                  \
+  launch_plain(gated_group_norm_kernel<T, VEC, FIRST>, grid, dim3(kThreads), 0, stream, y, (const T*)z, z_stride, w, (T*)out, \
+               n, n / parts, eps)
+#define EMBER_GGN(T, VEC) (gate_first ? EMBER_GGN1(T, VEC, true) : EMBER_GGN1(T, VEC, false))
   if (dtype == EMBER_F32)
     e = vec ? EMBER_GGN(float, true) : EMBER_GGN(float, false);
   else if (dtype == EMBER_BF16)
@@ -280,6 +286,7 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
   else
     return ember_fail("gated_group_norm: element type %d", dtype);
 #undef EMBER_GGN
+#undef EMBER_GGN1
   if (e != cudaSuccess) return ember_fail("gated_group_norm: %s", cudaGetErrorString(e));
   return 0;
 }

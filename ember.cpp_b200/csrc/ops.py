@@ -59,7 +59,7 @@ _SIGNATURES = {
     "ember_add_normed": [_c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_float, _c_float, _c_void],
     "ember_gated_act": [_c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_float, _c_int, _c_void],
     "ember_gated_group_norm": [_c_void, _c_void, ctypes.c_longlong, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float,
-                               _c_int, _c_void],
+                               _c_int, _c_int, _c_void],
     "ember_kv_store_v": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_int, _c_void],
     "ember_attention_plain_v": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
@@ -79,6 +79,18 @@ _SIGNATURES = {
                           _c_int, _c_int, _c_void],
     "ember_moe_down": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_void],
+    "ember_pair_table_add": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                             ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void],
+    "ember_rotate": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_int,
+                     _c_int, _c_int, _c_int, _c_void, _c_void, _c_float, _c_int, _c_void],
+    "ember_latent_rows": [_c_void, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_float, _c_void, _c_float, _c_int,
+                          _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+    "ember_head_linear": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, ctypes.c_longlong, _c_int, _c_int,
+                          _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_latent_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
+                                     _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_delta_rule": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
+                         _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
 }
 
@@ -138,6 +150,8 @@ def load_library() -> ctypes.CDLL:
     lib.ember_ssd_pieces_len.restype = _c_int
     lib.ember_ssd_scan_scratch.argtypes = [_c_int] * 5
     lib.ember_ssd_scan_scratch.restype = _c_size
+    lib.ember_delta_rule_scratch.argtypes = [_c_int] * 4
+    lib.ember_delta_rule_scratch.restype = _c_size
     lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
     lib.ember_attention_decode_kept_scratch.restype = _c_size
     for name in ("ember_tc_status", "ember_linear_decode_status", "ember_attention_decode_status",
@@ -793,16 +807,114 @@ class CudaOps:
                    self._ptr(scratch), _code(xbc.dtype))
         return y
 
-    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype):
+    def gated_group_norm(self, y, proj, z_col, w, parts, eps, out_dtype, gate_first=True):
         """unit(y * silu(z)) * w with the root mean square over each of `parts` equal pieces of a row; z: the
-        columns from z_col of `proj`."""
+        columns from z_col of `proj`.  gate_first False: unit(y) * w * silu(z), the gate after the norm."""
         rows, n = y.shape
         if y.dtype != torch.float32 or proj.dtype != out_dtype or z_col + n > proj.shape[1] or w.shape[0] != n:
             raise KernelError("gated_group_norm: float32 y, the gate in the output's element type, a gain of y's width")
         out = torch.empty((rows, n), dtype=out_dtype, device=y.device)
         z = proj[:, z_col:]
         self._call("ember_gated_group_norm", self._dense(y, "y").data_ptr(), z.data_ptr(), proj.stride(0), w.data_ptr(),
-                   out.data_ptr(), rows, n, int(parts), float(eps), _code(out_dtype))
+                   out.data_ptr(), rows, n, int(parts), float(eps), 1 if gate_first else 0, _code(out_dtype))
+        return out
+
+    # ------------------------------------------------------------------ a table of token pairs
+    def pair_table_add(self, x, plan, table, state, mul_prev, mul_cur, buckets):
+        """x[t] += table[row] in place, row = (token before * mul_prev + token * mul_cur) mod buckets, or the table's
+        last row for a sequence's first token; state int32 [slots, 1]: each sequence's last token so far (advanced)."""
+        T, d = x.shape
+        if x.dtype != torch.float32 or table.shape != (buckets + 1, d) or state.dtype != torch.int32:
+            raise KernelError("pair_table_add: a float32 stream, a table of buckets + 1 rows of its width, int32 state")
+        self._call("ember_pair_table_add", self._dense(x, "stream").data_ptr(), plan.tokens.data_ptr(), plan.positions.data_ptr(),
+                   plan.token_seq.data_ptr(), plan.seq_slot.data_ptr(), plan.cu_new.data_ptr(),
+                   self._dense(table, "pair table").data_ptr(), self._dense(state, "state").data_ptr(), T, d, int(mul_prev),
+                   int(mul_cur), int(buckets), 1 << 30, _code(table.dtype))
+        return x
+
+    # ------------------------------------------------------------------ rotation, rows of low rank, products per head
+    def rotate(self, src, dst, positions, heads, src_col, src_head, dst_col, dst_head, width, freqs, magnitude, dims):
+        """For every token t and head h < heads: `width` values from column src_col + h * src_head of src, their first
+        `dims` rotated by the token's position (pair i with i + dims / 2, angle position * freqs[i], cos and sin times
+        `magnitude`), written to column dst_col + h * dst_head of dst.  src and dst may be one tensor."""
+        T = src.shape[0]
+        if src.stride(1) != 1 or dst.stride(1) != 1 or dst.shape[0] != T or freqs.dtype != torch.float32 or freqs.numel() != dims // 2:
+            raise KernelError("rotate: rows of contiguous values, a float32 frequency for every pair")
+        if src_col + (heads - 1) * src_head + width > src.shape[1] or dst_col + (heads - 1) * dst_head + width > dst.shape[1]:
+            raise KernelError("rotate: the heads do not fit the rows")
+        self._call("ember_rotate", src.data_ptr(), src.stride(0), int(src_col), int(src_head), _code(src.dtype), dst.data_ptr(),
+                   dst.stride(0), int(dst_col), int(dst_head), _code(dst.dtype), T, int(heads), int(width),
+                   positions.data_ptr(), freqs.data_ptr(), float(magnitude), int(dims))
+        return dst
+
+    def latent_rows(self, down, plan, q_rank, q_norm, kv_norm, kv_rank, rot_dim, eps, rotary, cache, out_dtype):
+        """From float32 rows [T, q_rank (| kv_rank | rot_dim)]: the RMS-normed query row (returned, `out_dtype`), and with
+        a cache the RMS-normed row c and the rotated key part, written at each token's position into the cache's key
+        and value pages."""
+        T, width = down.shape
+        if down.dtype != torch.float32 or q_norm.shape[0] != q_rank:
+            raise KernelError("latent_rows: float32 rows and a gain of the query row's width")
+        c_q = torch.empty((T, q_rank), dtype=out_dtype, device=down.device)
+        if cache is not None:
+            if cache.k.dtype != out_dtype or tuple(cache.k.shape[1:]) != (1, 64, kv_rank) or tuple(cache.v.shape[1:]) != (1, 64, rot_dim):
+                raise KernelError("latent_rows: the cache's pages do not have the mixer's row sizes or element type")
+            if kv_norm.shape[0] != kv_rank:
+                raise KernelError("latent_rows: a gain of the cached row's width")
+        pages = None if cache is None else plan.pages[cache.group_index]
+        self._call("ember_latent_rows", self._dense(down, "rows").data_ptr(), width, int(q_rank), q_norm.data_ptr(),
+                   self._ptr(kv_norm), int(kv_rank), int(rot_dim), float(eps), rotary.freqs.data_ptr(), float(rotary.magnitude),
+                   int(rotary.dims), c_q.data_ptr(), None if cache is None else cache.k.data_ptr(),
+                   None if cache is None else cache.v.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(),
+                   plan.seq_slot.data_ptr(), self._ptr(pages), plan.max_blocks, T, _code(out_dtype))
+        return c_q
+
+    def head_linear(self, a, a_col, a_head, w, out, out_col, out_head):
+        """out[t, out_col + h * out_head + (0..N)] = a[t, a_col + h * a_head + (0..K)] w[h]^T for every head h of
+        w [heads, N, K]; float32 sums."""
+        heads, N, K = w.shape
+        T = a.shape[0]
+        if a.dtype != w.dtype or out.dtype != w.dtype or out.shape[0] != T or a.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("head_linear: rows, matrices and output of one element type")
+        if a_col + (heads - 1) * a_head + K > a.shape[1] or out_col + (heads - 1) * out_head + N > out.shape[1]:
+            raise KernelError("head_linear: the heads do not fit the rows")
+        self._call("ember_head_linear", a.data_ptr(), a.stride(0), int(a_col), int(a_head), self._dense(w, "matrices").data_ptr(),
+                   out.data_ptr(), out.stride(0), int(out_col), int(out_head), T, heads, N, K, _code(w.dtype))
+        return out
+
+    def latent_attention(self, rows, cache, plan, heads, kv_rank, rot_dim, scale, out_dtype):
+        """Causal attention of the step's query heads (each `kv_rank` values for the cached rows, then `rot_dim` for the
+        shared key part) over the cache; per head the weighted sum of the cached rows: [T, heads * kv_rank]."""
+        T = rows.shape[0]
+        if rows.dtype != cache.k.dtype or out_dtype != rows.dtype or rows.shape[1] != heads * (kv_rank + rot_dim):
+            raise KernelError("latent_attention: query rows, cache and output of one element type and fitting sizes")
+        if tuple(cache.k.shape[1:]) != (1, 64, kv_rank) or tuple(cache.v.shape[1:]) != (1, 64, rot_dim):
+            raise KernelError("latent_attention: the cache's pages do not have the mixer's row sizes")
+        out = torch.empty((T, heads * kv_rank), dtype=out_dtype, device=rows.device)
+        pages = plan.pages[cache.group_index]
+        self._call("ember_latent_attention_plain", self._dense(rows, "query rows").data_ptr(), cache.k.data_ptr(),
+                   cache.v.data_ptr(), out.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(),
+                   plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, T, heads, kv_rank, rot_dim, float(scale),
+                   _code(rows.dtype))
+        return out
+
+    # ------------------------------------------------------------------ gated delta rule
+    def delta_rule(self, qkv, proj, b_col, a_col, a_log, dt_bias, state, plan, heads, kv_heads, dim, vdim, unit_eps):
+        """The recurrence of parts/delta.py over the step's sequences: qkv [T, q | k | v] (the convolution's output),
+        the raw beta and step in `heads` columns each from b_col and a_col of `proj`, state float32
+        [slots, heads, dim, vdim] (advanced); float32 o [T, heads * vdim]."""
+        T = qkv.shape[0]
+        if qkv.shape[1] != 2 * kv_heads * dim + heads * vdim or qkv.dtype != proj.dtype:
+            raise KernelError("delta_rule: rows of q | k | v in the projection's element type")
+        if state.dtype != torch.float32 or tuple(state.shape[1:]) != (heads, dim, vdim):
+            raise KernelError("delta_rule: the state is float32 [slots, heads, dim, vdim]")
+        self._dense(qkv, "q | k | v")
+        out = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkv.device)
+        scratch = torch.empty(self.lib.ember_delta_rule_scratch(T, heads, kv_heads, dim), dtype=torch.float32, device=qkv.device)
+        self._call("ember_delta_rule", qkv.data_ptr(), proj.data_ptr(), proj.stride(0), int(b_col), int(a_col), a_log.data_ptr(),
+                   dt_bias.data_ptr(), state.data_ptr(), out.data_ptr(), scratch.data_ptr(), plan.seq_slot.data_ptr(),
+                   plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), T, plan.n, heads, kv_heads, dim, vdim, float(unit_eps),
+                   _code(qkv.dtype))
+        self.launches += 1      # (the prepare kernel)
         return out
 
     # ------------------------------------------------------------------ experts by table
