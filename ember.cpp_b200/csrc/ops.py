@@ -89,6 +89,8 @@ _SIGNATURES = {
                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
     "ember_latent_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+    "ember_latent_attention_mma": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
+                                   _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ember_delta_rule": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
                          _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
@@ -150,6 +152,8 @@ def load_library() -> ctypes.CDLL:
     lib.ember_ssd_pieces_len.restype = _c_int
     lib.ember_ssd_scan_scratch.argtypes = [_c_int] * 5
     lib.ember_ssd_scan_scratch.restype = _c_size
+    lib.ember_latent_attention_mma_scratch.argtypes = [_c_int] * 3
+    lib.ember_latent_attention_mma_scratch.restype = _c_size
     lib.ember_delta_rule_scratch.argtypes = [_c_int] * 4
     lib.ember_delta_rule_scratch.restype = _c_size
     lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
@@ -233,6 +237,10 @@ class CudaOps:
         #   kernel and the split one-token kernel where they have the sizes; False takes the plain kernel everywhere
         #   (a measurement switch: the twin that the two are compared with)
         self.attention_kept_fast = True
+        # latent_fast: attention over cached low-rank rows in bfloat16 takes the tensor-core kernel where it has the
+        #   sizes; False takes the plain kernel everywhere (the twin that it is compared with)
+        self.latent_fast = True
+        self.latent_pages_per_chunk = 0    # pages a block of its one-token form takes; 0: as many as fill the chip about twice
         # branch_streams: `side_by_side` runs independent branches of a one-token step on streams of their own
         self.branch_streams = options.branch_streams
         self._side_streams = []
@@ -891,6 +899,24 @@ class CudaOps:
             raise KernelError("latent_attention: the cache's pages do not have the mixer's row sizes")
         out = torch.empty((T, heads * kv_rank), dtype=out_dtype, device=rows.device)
         pages = plan.pages[cache.group_index]
+        if self.latent_fast and rows.dtype == torch.bfloat16:
+            # one token each: the pages in chunks, a block a chunk, so that the launch fills the chip about twice
+            blocks = min(plan.max_blocks, max(1, -(-plan.max_end // 64)))
+            n_chunks, per_chunk = 1, plan.max_blocks
+            if plan.all_single and plan.T == plan.n:
+                tiles = plan.n * -(-heads // 64)
+                n_chunks = max(1, min(blocks, 2 * self.sms // max(tiles, 1)))
+                per_chunk = self.latent_pages_per_chunk or -(-blocks // n_chunks)
+                n_chunks = -(-blocks // per_chunk)
+            n_scratch = self.lib.ember_latent_attention_mma_scratch(T * heads, kv_rank, n_chunks)
+            scratch = torch.empty(n_scratch, dtype=torch.float32, device=rows.device) if n_scratch else None
+            rc = self._call("ember_latent_attention_mma", self._dense(rows, "query rows").data_ptr(), cache.k.data_ptr(),
+                            cache.v.data_ptr(), out.data_ptr(), self._ptr(scratch), plan.seq_slot.data_ptr(),
+                            plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), pages.data_ptr(), plan.max_blocks, plan.n,
+                            max(int(plan.max_new), 1), T, heads, kv_rank, rot_dim, float(scale), n_chunks, per_chunk, allow=(2,))
+            if rc == 0:
+                self.launches += 1 if n_chunks > 1 else 0      # (the merge)
+                return out
         self._call("ember_latent_attention_plain", self._dense(rows, "query rows").data_ptr(), cache.k.data_ptr(),
                    cache.v.data_ptr(), out.data_ptr(), plan.positions.data_ptr(), plan.token_seq.data_ptr(),
                    plan.seq_slot.data_ptr(), pages.data_ptr(), plan.max_blocks, T, heads, kv_rank, rot_dim, float(scale),

@@ -153,7 +153,12 @@ def test_the_stream_after_every_layer(folders, plains):
     seen = []
     for block in eng.model.blocks:
         inner = block.forward
-        block.forward = lambda ctx, x, app, inner=inner: seen.append(inner(ctx, x, app).clone()) or seen[-1]
+
+        def hooked(ctx, x, app, inner=inner):
+            out = inner(ctx, x, app)
+            seen.append(out.clone())          # (a copy: the next layer adds into the stream in place)
+            return out
+        block.forward = hooked
     slot = eng.open()
     eng.step([(slot, seq, [])])
     assert len(seen) == len(streams)
