@@ -225,8 +225,36 @@ DESIGN_SIZES = {
 }
 
 
-def design_configs(size: str):
-    """(Nipolorn configuration, GPT-2 configuration of equal width, layers, heads and dense inner size)."""
+MUZOZEN_SIZES = {
+    # attention over cached rows: heads / plain / rotated / value dimensions, query and cached rank; delta rule: heads / key heads / dim / vdim
+    "small": dict(heads=16, dim=64, rot=32, vdim=64, q_rank=384, kv_rank=256, d_heads=16, d_kv=8, d_dim=64, d_vdim=64),
+    "medium": dict(heads=16, dim=128, rot=64, vdim=128, q_rank=768, kv_rank=512, d_heads=16, d_kv=8, d_dim=128, d_vdim=128),
+}
+
+
+def muzozen_config(size: str):
+    """A Muzozen of the width, layer count, dense inner size and vocabulary of `DESIGN_SIZES[size]`: attention over cached
+    rows, a delta-rule layer, an attention layer that reads the first layer's rows, and so on in turn."""
+    z, m = DESIGN_SIZES[size], MUZOZEN_SIZES[size]
+    rot = {"dims": m["rot"], "base": 10000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    latent = {"heads": m["heads"], "dim": m["dim"], "rot_dim": m["rot"], "vdim": m["vdim"], "q_rank": m["q_rank"],
+              "kv_rank": m["kv_rank"], "scale": (m["dim"] + m["rot"]) ** -0.5, "rot": rot}
+    delta = {"heads": m["d_heads"], "kv_heads": m["d_kv"], "dim": m["d_dim"], "vdim": m["d_vdim"], "conv": 4}
+    layers = []
+    for i in range(z["layers"]):
+        kind = ("latent_attention", dict(latent)) if i % 2 == 0 else ("delta", dict(delta))
+        if i % 4 == 2:
+            kind[1]["kv_from"] = i - 2
+        layers.append({"type": kind[0], "mixer": kind[1], "mlp": {"kind": "dense", "ff": z["ff"]}})
+    return {"architecture": "Muzozen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.5, "bigram": {"buckets": 100003, "mul_prev": 1000003, "mul_cur": 31}}, "layers": layers}
+
+
+def design_configs(size: str, design: str = "nipolorn"):
+    """(Nipolorn configuration, GPT-2 configuration of equal width, layers, heads and dense inner size); for Muzozen
+    its configuration in front of the two."""
+    if design == "muzozen":
+        return (muzozen_config(size),) + design_configs(size)
     z = DESIGN_SIZES[size]
     left = {"dim": z["dim"], "vdim": z["dim"], "heads": z["heads"], "kv_heads": z["kv_heads"], "scale": z["dim"] ** -0.5,
             "mask": {"size": z["window"], "keep_first": z["keep"]}}
@@ -242,7 +270,7 @@ def design_configs(size: str):
 
 
 def design_mode(args) -> int:
-    """Prefill and decode throughput of a Nipolorn model beside a GPT-2 of equal width, layers, head size and dense
+    """Prefill and decode throughput of a Nipolorn (or, with `--design muzozen`, of a Muzozen and a Nipolorn) model beside a GPT-2 of equal width, layers, head size and dense
     inner size, both with random bfloat16 weights: a prompt of `--prompt-len` tokens (default 2,048) in one step,
     and one-token steps of `--batch` sequences at that context; CUDA-event times, the median of five prompts and the
     mean of `--steps` replayed steps after `--warmup`.  Then the same two steps launch by launch with an event
@@ -261,7 +289,7 @@ def design_mode(args) -> int:
     B, K, W = args.batch, args.steps or 64, max(3, args.warmup)
     rng = np.random.default_rng(0)
     pk = peaks()
-    for cfgd in design_configs(args.design_size):
+    for cfgd in design_configs(args.design_size, args.design):
         config = config_from_dict(cfgd)
         spec = get_architecture(config.architecture).build_spec(config)
         tensors = random_tensors(DecoderModel(spec).weight_specs(), seed=0, dtype=torch.bfloat16, device="cuda")
@@ -360,8 +388,9 @@ def main() -> int:
                     help="time one bfloat16 product on every kernel that takes it, instead of the benchmark")
     ap.add_argument("--act", default=None, choices=[None, "gelu_tanh", "gelu_erf"], help="with --linear: the epilogue's activation")
     ap.add_argument("--residual", action="store_true", help="with --linear: add a float32 residual (the output is float32 then)")
-    ap.add_argument("--design", default=None, choices=["nipolorn"],
-                    help="instead of the benchmark: prefill and decode throughput of this design beside a GPT-2 of equal size")
+    ap.add_argument("--design", default=None, choices=["nipolorn", "muzozen"],
+                    help="instead of the benchmark: prefill and decode throughput of this design beside a GPT-2 of equal size "
+                         "(muzozen: beside a Nipolorn and a GPT-2 of equal size)")
     ap.add_argument("--design-size", default="medium", choices=sorted(DESIGN_SIZES), help="with --design: the layers' sizes")
     ap.add_argument("--umma-issue", action="store_true", help="print what a tcgen05.mma costs to issue, by shape and way of issuing")
     args = ap.parse_args()

@@ -23,8 +23,9 @@ __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log
 template <typename T>
 __global__ void delta_prepare_kernel(const T* __restrict__ qkv, const T* __restrict__ proj, long long proj_stride, int b_col,
                                      int a_col, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
-                                     float* __restrict__ qk, float* __restrict__ beta, float* __restrict__ decay, int heads,
-                                     int kv_heads, int dim, int channels, float unit_eps) {
+                                     float* __restrict__ qk, float* __restrict__ beta, float* __restrict__ decay,
+                                     float* __restrict__ log_decay, int heads, int kv_heads, int dim, int channels,
+                                     float unit_eps) {
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const T* row = qkv + (size_t)t * channels;
   const float q_scale = rsqrtf((float)dim);
@@ -43,11 +44,14 @@ __global__ void delta_prepare_kernel(const T* __restrict__ qkv, const T* __restr
     const float b = to_float(proj[(size_t)t * proj_stride + b_col + h]);
     const float a = to_float(proj[(size_t)t * proj_stride + a_col + h]);
     beta[(size_t)t * heads + h] = 1.0f / (1.0f + expf(-b));
-    decay[(size_t)t * heads + h] = expf(-expf(a_log[h]) * softplus_f(a + dt_bias[h]));
+    const float lg = -expf(a_log[h]) * softplus_f(a + dt_bias[h]);
+    decay[(size_t)t * heads + h] = expf(lg);
+    log_decay[(size_t)t * heads + h] = lg;
   }
 }
 
 constexpr int kStage = 16;   // tokens staged in shared memory at a time
+inline size_t align4(size_t n) { return (n + 3) & ~(size_t)3; }
 
 // grid (sequences, heads, column tiles), blockDim.x columns a block.  DMAX >= dim: the column's registers.
 template <typename T, int DMAX>
@@ -183,18 +187,257 @@ __global__ void delta_scan_wide_kernel(const float* __restrict__ qk, const T* __
   }
 }
 
+
+// ---------------------------------------------------------------------------- prompts in chunks of 64 tokens
+// Inside a chunk the rule has a closed form.  With L_t the sum of log g over the chunk's tokens up to t, and S0 the
+// state at the chunk's start, the writes u_t of the chunk solve (I + A) U = diag(beta) V - diag(beta e^L) K S0 with
+// A[t][i] = beta_t e^(L_t - L_i) (k_t . k_i) for i < t.  So with Tm = (I + A)^-1 (unit lower triangular),
+//     Wv = Tm diag(beta) V,   Wk = Tm diag(beta e^L) K,   P[t][i] = e^(L_t - L_i) (q_t . k_i) for i <= t
+// depend on the chunk alone (`delta_chunk_factor`, a block a (chunk, head), all chunks side by side), and then
+//     U = Wv - Wk S0,   O = diag(e^L) Q S0 + P U,   S <- e^(L_end) S0 + sum_i e^(L_end - L_i) k_i u_i^T
+// walk the chunks in order (`delta_chunk_scan`, a block a (sequence, head, 32 value columns): the columns of S are
+// independent).  Every exponent is of a difference <= 0.  All float32 on the CUDA cores; a chunk's rows past the
+// sequence's end count as beta = 0, g = 1 and zero vectors.
+constexpr int kChunk = 64;
+constexpr int kTile = 32;    // value columns a block of the scan
+
+// The chunk slot of sequence s's chunk c: chunks are numbered through the step's sequences in order.
+__device__ __forceinline__ int chunk_slot(const int* cu_new, int s, int c) {
+  int base = 0;
+  for (int i = 0; i < s; ++i) base += (cu_new[i + 1] - cu_new[i] + kChunk - 1) / kChunk;
+  return base + c;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_chunk_factor_kernel(const float* __restrict__ qk, const T* __restrict__ qkv, const float* __restrict__ beta,
+                          const float* __restrict__ log_decay, float* __restrict__ wv, float* __restrict__ wk,
+                          float* __restrict__ pm, float* __restrict__ lgc, const int* __restrict__ seq_slot,
+                          const int* __restrict__ cu_new, int n_seq, int max_chunks, int heads, int kv_heads, int dim, int vdim,
+                          int channels) {
+  extern __shared__ float sm[];
+  const int s = blockIdx.x / max_chunks, c = blockIdx.x % max_chunks, h = blockIdx.y;
+  const int t0 = cu_new[s], n = cu_new[s + 1] - t0;
+  if (seq_slot[s] < 0 || c * kChunk >= n) return;
+  const int rows = min(kChunk, n - c * kChunk), first = t0 + c * kChunk;
+  const int kh = h / (heads / kv_heads), qk_row = 2 * kv_heads * dim, DS = dim + 1, CS = kChunk + 1;
+  float* ks = sm;                       // [64][dim + 1]
+  float* qs = ks + kChunk * DS;         // [64][dim + 1]
+  float* am = qs + kChunk * DS;         // [64][65]: A, then Tm scaled for Wk
+  float* tm = am + kChunk * CS;         // [64][65]: Tm
+  float* lg = tm + kChunk * CS;         // [64] L_t
+  float* bt = lg + kChunk;              // [64] beta_t
+  float* raw = bt + kChunk;             // [64] log g_t
+  const int tid = threadIdx.x;
+  if (tid < kChunk) {
+    raw[tid] = tid < rows ? log_decay[(size_t)(first + tid) * heads + h] : 0.f;
+    bt[tid] = tid < rows ? beta[(size_t)(first + tid) * heads + h] : 0.f;
+  }
+  for (int e = tid; e < kChunk * dim; e += 256) {
+    const int r = e / dim, d = e % dim;
+    const float* src = qk + (size_t)(first + r) * qk_row;
+    qs[r * DS + d] = r < rows ? src[(size_t)kh * dim + d] : 0.f;
+    ks[r * DS + d] = r < rows ? src[(size_t)(kv_heads + kh) * dim + d] : 0.f;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float run = 0.f;
+    for (int r = 0; r < kChunk; ++r) {
+      run += raw[r];
+      lg[r] = run;
+    }
+  }
+  __syncthreads();
+  const size_t slot = ((size_t)chunk_slot(cu_new, s, c) * heads + h) * kChunk;
+  if (tid < kChunk) lgc[slot + tid] = lg[tid];
+  // A and P: thread (i = tid % 64, rows t = tid / 64 + 4 j)
+  {
+    const int i = tid & 63;
+    for (int t = tid >> 6; t < kChunk; t += 4) {
+      float kk = 0.f, qk_dot = 0.f;
+      for (int d = 0; d < dim; ++d) {
+        const float ki = ks[i * DS + d];
+        kk = fmaf(ks[t * DS + d], ki, kk);
+        qk_dot = fmaf(qs[t * DS + d], ki, qk_dot);
+      }
+      const float w = i <= t ? expf(lg[t] - lg[i]) : 0.f;
+      am[t * CS + i] = i < t ? bt[t] * w * kk : 0.f;
+      pm[(slot + t) * kChunk + i] = w * qk_dot;
+    }
+  }
+  __syncthreads();
+  // Tm = (I + A)^-1 by forward substitution, a thread a column (a column needs only itself)
+  if (tid < kChunk) {
+    const int col = tid;
+    for (int t = 0; t < kChunk; ++t) {
+      float v = t == col ? 1.f : 0.f;
+      for (int i = col; i < t; ++i) v = fmaf(-am[t * CS + i], tm[i * CS + col], v);   // (rows above `col` are zero)
+      tm[t * CS + col] = t >= col ? v : 0.f;
+    }
+  }
+  __syncthreads();
+  // columns scaled: tm <- Tm diag(beta), am <- Tm diag(beta e^L)
+  for (int e = tid; e < kChunk * kChunk; e += 256) {
+    const int r = e >> 6, i = e & 63;
+    const float v = tm[r * CS + i] * bt[i];
+    tm[r * CS + i] = v;
+    am[r * CS + i] = v * expf(lg[i]);
+  }
+  __syncthreads();
+  const int rg = tid >> 5, lane = tid & 31;
+  for (int c0 = 0; c0 < vdim; c0 += 32) {   // Wv: rows rg + 8 j, column c0 + lane
+    const int col = c0 + lane;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < rows; ++i) {
+      const float v = col < vdim ? to_float(qkv[(size_t)(first + i) * channels + 2 * kv_heads * dim + (size_t)h * vdim + col]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(tm[(rg + 8 * j) * CS + i], v, acc[j]);
+    }
+    if (col < vdim)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wv[(slot + rg + 8 * j) * vdim + col] = acc[j];
+  }
+  for (int c0 = 0; c0 < dim; c0 += 32) {    // Wk
+    const int col = c0 + lane;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < rows; ++i) {
+      const float v = col < dim ? ks[i * DS + col] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(am[(rg + 8 * j) * CS + i], v, acc[j]);
+    }
+    if (col < dim)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) wk[(slot + rg + 8 * j) * dim + col] = acc[j];
+  }
+}
+
+__global__ void __launch_bounds__(256)
+delta_chunk_scan_kernel(const float* __restrict__ qk, const float* __restrict__ wv, const float* __restrict__ wk,
+                        const float* __restrict__ pm, const float* __restrict__ lgc, float* __restrict__ state,
+                        float* __restrict__ out, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
+                        const int* __restrict__ cu_new, int n_seq, int heads, int kv_heads, int dim, int vdim) {
+  extern __shared__ __align__(16) float sm[];
+  float* wks = sm;                          // [64][dim]
+  float* qs = wks + kChunk * dim;           // [64][dim]
+  float* ks = qs + kChunk * dim;            // [64][dim]
+  float* ps = ks + kChunk * dim;            // [64][64]
+  float* us = ps + kChunk * kChunk;         // [64][32]: Wv's columns, then U
+  float* ss = us + kChunk * kTile;          // [dim][32]: the state's columns
+  float* lg = ss + dim * kTile;             // [64] L_t
+  float* wj = lg + kChunk;                  // [64] e^(L_end - L_t)
+  const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kTile;
+  const int tid = threadIdx.x, lane = tid & 31, rg = tid >> 5;
+  const int col = c0 + lane;
+  const bool live = col < vdim;
+  const int t0 = cu_new[s], n = cu_new[s + 1] - t0;
+  const int slot = seq_slot[s];
+  const int inner = heads * vdim;
+  if (slot < 0) {
+    if (live)
+      for (int i = rg; i < n; i += 8) out[(size_t)(t0 + i) * inner + (size_t)h * vdim + col] = 0.f;
+    return;
+  }
+  const int kh = h / (heads / kv_heads), qk_row = 2 * kv_heads * dim;
+  float* st = state + ((size_t)slot * heads + h) * dim * vdim;
+  const bool carried = seq_start[s] > 0;
+  for (int d = rg; d < dim; d += 8) ss[d * kTile + lane] = (live && carried) ? st[(size_t)d * vdim + col] : 0.f;
+  const int base = chunk_slot(cu_new, s, 0);
+  const int n_chunks = (n + kChunk - 1) / kChunk;
+  for (int c = 0; c < n_chunks; ++c) {
+    const int rows = min(kChunk, n - c * kChunk), first = t0 + c * kChunk;
+    const size_t cs = ((size_t)(base + c) * heads + h) * kChunk;
+    __syncthreads();   // the chunk before is done with the tiles
+    for (int e = tid * 4; e < kChunk * dim; e += 1024) {
+      const int r = e / dim, d = e % dim;
+      *reinterpret_cast<float4*>(wks + e) = *reinterpret_cast<const float4*>(wk + cs * dim + e);
+      const float* src = qk + (size_t)(first + r) * qk_row;
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      *reinterpret_cast<float4*>(qs + e) = r < rows ? *reinterpret_cast<const float4*>(src + (size_t)kh * dim + d) : zero;
+      *reinterpret_cast<float4*>(ks + e) = r < rows ? *reinterpret_cast<const float4*>(src + (size_t)(kv_heads + kh) * dim + d) : zero;
+    }
+    for (int e = tid * 4; e < kChunk * kChunk; e += 1024)
+      *reinterpret_cast<float4*>(ps + e) = *reinterpret_cast<const float4*>(pm + cs * kChunk + e);
+    for (int r = rg; r < kChunk; r += 8) us[r * kTile + lane] = live ? wv[(cs + r) * vdim + col] : 0.f;
+    if (tid < kChunk) lg[tid] = lgc[cs + tid];
+    __syncthreads();
+    if (tid < kChunk) wj[tid] = tid < rows ? expf(lg[kChunk - 1] - lg[tid]) : 0.f;
+    // U = Wv - Wk S0 and Q S0 for rows rg + 8 j
+    float au[8], aq[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) au[j] = aq[j] = 0.f;
+    for (int d = 0; d < dim; d += 4) {
+      const float s0 = ss[d * kTile + lane], s1 = ss[(d + 1) * kTile + lane], s2 = ss[(d + 2) * kTile + lane],
+                  s3 = ss[(d + 3) * kTile + lane];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 w = *reinterpret_cast<const float4*>(wks + (rg + 8 * j) * dim + d);
+        const float4 qv = *reinterpret_cast<const float4*>(qs + (rg + 8 * j) * dim + d);
+        au[j] = fmaf(w.x, s0, fmaf(w.y, s1, fmaf(w.z, s2, fmaf(w.w, s3, au[j]))));
+        aq[j] = fmaf(qv.x, s0, fmaf(qv.y, s1, fmaf(qv.z, s2, fmaf(qv.w, s3, aq[j]))));
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) us[(rg + 8 * j) * kTile + lane] -= au[j];
+    __syncthreads();
+    // O = e^L (Q S0) + P U
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int r = rg + 8 * j;
+      float o = expf(lg[r]) * aq[j];
+      for (int i = 0; i <= r; ++i) o = fmaf(ps[r * kChunk + i], us[i * kTile + lane], o);
+      if (live && r < rows) out[(size_t)(first + r) * inner + (size_t)h * vdim + col] = o;
+    }
+    // S <- e^(L_end) S0 + sum_i e^(L_end - L_i) k_i u_i^T for the state's rows rg + 8 j
+    const float tail = expf(lg[kChunk - 1]);
+    for (int d = rg; d < dim; d += 8) {
+      float v = tail * ss[d * kTile + lane];
+      for (int i = 0; i < rows; ++i) v = fmaf(wj[i] * ks[i * dim + d], us[i * kTile + lane], v);
+      ss[d * kTile + lane] = v;
+    }
+  }
+  __syncthreads();
+  if (live)
+    for (int d = rg; d < dim; d += 8) st[(size_t)d * vdim + col] = ss[d * kTile + lane];
+}
+
 template <typename T>
 int delta_rule_run(const T* qkv, const T* proj, long long proj_stride, int b_col, int a_col, const float* a_log,
                    const float* dt_bias, float* state, float* out, float* scratch, const int* seq_slot, const int* seq_start,
                    const int* cu_new, int T_tokens, int n_seq, int heads, int kv_heads, int dim, int vdim, float unit_eps,
-                   cudaStream_t stream) {
+                   int max_new, int chunk_slots, cudaStream_t stream) {
   const int channels = 2 * kv_heads * dim + heads * vdim;
-  float* qk = scratch;
-  float* beta = qk + (size_t)T_tokens * 2 * kv_heads * dim;
-  float* decay = beta + (size_t)T_tokens * heads;
+  float* qk = scratch;                                                       // (every part starts on 16 bytes)
+  float* beta = qk + align4((size_t)T_tokens * 2 * kv_heads * dim);
+  float* decay = beta + align4((size_t)T_tokens * heads);
+  float* log_decay = decay + align4((size_t)T_tokens * heads);
   delta_prepare_kernel<T><<<T_tokens, 128, 0, stream>>>(qkv, proj, proj_stride, b_col, a_col, a_log, dt_bias, qk, beta, decay,
-                                                        heads, kv_heads, dim, channels, unit_eps);
+                                                        log_decay, heads, kv_heads, dim, channels, unit_eps);
   EMBER_LAUNCH_OK("delta_prepare");
+  if (chunk_slots > 0) {
+    const int max_chunks = (max_new + kChunk - 1) / kChunk;
+    float* wv = log_decay + align4((size_t)T_tokens * heads);               // [chunk slots][heads][64][vdim]
+    float* wk = wv + (size_t)chunk_slots * heads * kChunk * vdim;           // [chunk slots][heads][64][dim]
+    float* pm = wk + (size_t)chunk_slots * heads * kChunk * dim;            // [chunk slots][heads][64][64]
+    float* lgc = pm + (size_t)chunk_slots * heads * kChunk * kChunk;        // [chunk slots][heads][64]: the sums of logarithms
+    const size_t smem1 = (size_t)(2 * kChunk * (dim + 1) + 2 * kChunk * (kChunk + 1) + 3 * kChunk) * sizeof(float);
+    const size_t smem2 = (size_t)(3 * kChunk * dim + kChunk * kChunk + kChunk * kTile + dim * kTile + 2 * kChunk) * sizeof(float);
+    static bool raised[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!raised[dev & 63]) {
+      if (cudaFuncSetAttribute(delta_chunk_factor_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
+          cudaFuncSetAttribute(delta_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+        return ember_fail("delta_rule: the chunk kernels' shared memory could not be raised");
+      raised[dev & 63] = true;
+    }
+    delta_chunk_factor_kernel<T><<<dim3(n_seq * max_chunks, heads), 256, smem1, stream>>>(
+        qk, qkv, beta, log_decay, wv, wk, pm, lgc, seq_slot, cu_new, n_seq, max_chunks, heads, kv_heads, dim, vdim, channels);
+    EMBER_LAUNCH_OK("delta_chunk_factor");
+    delta_chunk_scan_kernel<<<dim3(n_seq, heads, (vdim + kTile - 1) / kTile), 256, smem2, stream>>>(
+        qk, wv, wk, pm, lgc, state, out, seq_slot, seq_start, cu_new, n_seq, heads, kv_heads, dim, vdim);
+    EMBER_LAUNCH_OK("delta_chunk_scan");
+    return 0;
+  }
   const int cols = vdim >= 128 ? 128 : (vdim + 31) / 32 * 32;
   const dim3 grid(n_seq, heads, (vdim + cols - 1) / cols);
 #define EMBER_DELTA_SCAN(DMAX)                                                                                          \
@@ -220,8 +463,10 @@ int delta_rule_run(const T* qkv, const T* proj, long long proj_stride, int b_col
 }  // namespace
 
 // floats of scratch for a step of T tokens: the unit vectors q | k per key head, beta and the decay per head
-EMBER_API size_t ember_delta_rule_scratch(int T, int heads, int kv_heads, int dim) {
-  return (size_t)T * (2 * (size_t)kv_heads * dim + 2 * (size_t)heads);
+// chunk_slots > 0 (the chunked form): room for that many chunks of 64 tokens more (see delta_rule_run)
+EMBER_API size_t ember_delta_rule_scratch(int T, int heads, int kv_heads, int dim, int vdim, int chunk_slots) {
+  return align4((size_t)T * 2 * kv_heads * dim) + 3 * align4((size_t)T * heads) +
+         (size_t)chunk_slots * heads * kChunk * ((size_t)vdim + dim + kChunk + 1);
 }
 
 // qkv [T, q | k | v] (the convolution's output), b and a: `heads` columns each from b_col and a_col of `proj`;
@@ -229,16 +474,19 @@ EMBER_API size_t ember_delta_rule_scratch(int T, int heads, int kv_heads, int di
 EMBER_API int ember_delta_rule(const void* qkv, const void* proj, long long proj_stride, int b_col, int a_col,
                                const float* a_log, const float* dt_bias, float* state, float* out, float* scratch,
                                const int* seq_slot, const int* seq_start, const int* cu_new, int T, int n_seq, int heads,
-                               int kv_heads, int dim, int vdim, float unit_eps, int dtype, cudaStream_t stream) {
+                               int kv_heads, int dim, int vdim, float unit_eps, int max_new, int chunk_slots, int dtype,
+                               cudaStream_t stream) {
+  EMBER_CHECK(chunk_slots == 0 || (dim % 4 == 0 && dim <= 128 && max_new > 0), "delta_rule: the chunked form takes key sizes "
+              "that are multiples of 4 up to 128 (here %d)", dim);
   EMBER_CHECK(T > 0 && n_seq > 0 && heads > 0 && kv_heads > 0 && dim > 0 && vdim > 0, "delta_rule: bad sizes");
   EMBER_CHECK(heads % kv_heads == 0, "delta_rule: %d heads are not a multiple of %d key heads", heads, kv_heads);
   EMBER_CHECK(heads <= 65535, "delta_rule: %d heads exceed one launch", heads);
   if (dtype == EMBER_F32)
     return delta_rule_run<float>((const float*)qkv, (const float*)proj, proj_stride, b_col, a_col, a_log, dt_bias, state, out,
-                                 scratch, seq_slot, seq_start, cu_new, T, n_seq, heads, kv_heads, dim, vdim, unit_eps, stream);
+                                 scratch, seq_slot, seq_start, cu_new, T, n_seq, heads, kv_heads, dim, vdim, unit_eps, max_new, chunk_slots, stream);
   if (dtype == EMBER_BF16)
     return delta_rule_run<__nv_bfloat16>((const __nv_bfloat16*)qkv, (const __nv_bfloat16*)proj, proj_stride, b_col, a_col,
                                          a_log, dt_bias, state, out, scratch, seq_slot, seq_start, cu_new, T, n_seq, heads,
-                                         kv_heads, dim, vdim, unit_eps, stream);
+                                         kv_heads, dim, vdim, unit_eps, max_new, chunk_slots, stream);
   return ember_fail("delta_rule: element type %d", dtype);
 }

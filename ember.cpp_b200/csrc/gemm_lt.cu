@@ -227,3 +227,103 @@ EMBER_API int ember_linear_bf16(const void* A, const void* W, const float* bias_
                         &plan.algo, workspace, workspace_bytes, stream));
   return 0;
 }
+
+// ---------------------------------------------------------------------------- one product per head
+// out[t, h * out_head + (0..N)] = a[t, h * a_head + (0..K)] . w[h]^T for every head h: the library's strided batch,
+// the heads side by side in the rows of `a` and `out` (a head's offset is the batch stride, a row's width the leading
+// dimension), w [heads, N, K].  bfloat16 in and out, float32 sums.  Returns 2 where the library offers no algorithm.
+namespace {
+struct HeadKey {
+  int T, N, K, heads;
+  long long a_stride, out_stride;
+  int a_head, out_head, align;
+  bool operator==(const HeadKey& o) const {
+    return T == o.T && N == o.N && K == o.K && heads == o.heads && a_stride == o.a_stride && out_stride == o.out_stride &&
+           a_head == o.a_head && out_head == o.out_head && align == o.align;
+  }
+};
+struct HeadHash {
+  size_t operator()(const HeadKey& k) const {
+    size_t h = 1469598103934665603ull;
+    const long long v[9] = {k.T, k.N, k.K, k.heads, k.a_stride, k.out_stride, k.a_head, k.out_head, k.align};
+    for (long long x : v) h = (h ^ (size_t)x) * 1099511628211ull;
+    return h;
+  }
+};
+std::unordered_map<HeadKey, Plan, HeadHash> g_head_plans;
+
+int lowest_bit_bytes(unsigned long long v) {   // the largest power of two up to 256 that divides v
+  int a = 256;
+  while (a > 1 && v % a) a >>= 1;
+  return a;
+}
+}  // namespace
+
+EMBER_API int ember_head_linear_bf16(const void* a, long long a_stride, int a_head, const void* w, void* out,
+                                     long long out_stride, int out_head, int T, int heads, int N, int K, void* workspace,
+                                     size_t workspace_bytes, cudaStream_t stream) {
+  EMBER_CHECK(T > 0 && heads > 0 && N > 0 && K > 0, "head_linear_bf16: bad sizes");
+  // what every pointer of the batch is a multiple of: the bases, the rows and the heads' offsets
+  int align = lowest_bit_bytes((unsigned long long)(uintptr_t)a | (unsigned long long)(uintptr_t)out |
+                               (unsigned long long)(uintptr_t)w | (unsigned long long)a_stride * 2 |
+                               (unsigned long long)out_stride * 2 | (unsigned long long)a_head * 2 |
+                               (unsigned long long)out_head * 2 | (unsigned long long)K * 2 | (unsigned long long)N * K * 2);
+  if (align < 16) return 2;
+  const HeadKey key{T, N, K, heads, a_stride, out_stride, a_head, out_head, align};
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_handle) LT_TRY(cublasLtCreate(&g_handle));
+  auto it = g_head_plans.find(key);
+  if (it == g_head_plans.end()) {
+    if (g_head_plans.size() >= kMaxPlans) {
+      for (auto& kv : g_head_plans) {
+        cublasLtMatmulDescDestroy(kv.second.op);
+        cublasLtMatrixLayoutDestroy(kv.second.a);
+        cublasLtMatrixLayoutDestroy(kv.second.b);
+        cublasLtMatrixLayoutDestroy(kv.second.c);
+      }
+      g_head_plans.clear();
+    }
+    Plan p;
+    LT_TRY(cublasLtMatmulDescCreate(&p.op, CUBLAS_COMPUTE_32F, CUDA_R_32F));
+    const cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
+    LT_TRY(cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof(ta)));
+    LT_TRY(cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof(tb)));
+    LT_TRY(cublasLtMatrixLayoutCreate(&p.a, CUDA_R_16BF, K, N, K));                 // w[h] as K x N, ld K
+    LT_TRY(cublasLtMatrixLayoutCreate(&p.b, CUDA_R_16BF, K, T, a_stride));          // a's head as K x T, ld a row
+    LT_TRY(cublasLtMatrixLayoutCreate(&p.c, CUDA_R_16BF, N, T, out_stride));        // out's head as N x T, ld a row
+    const int32_t batch = heads;
+    const int64_t sa = (int64_t)N * K, sb = a_head, sc = out_head;
+    LT_TRY(cublasLtMatrixLayoutSetAttribute(p.a, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &batch, sizeof(batch)));
+    LT_TRY(cublasLtMatrixLayoutSetAttribute(p.b, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &batch, sizeof(batch)));
+    LT_TRY(cublasLtMatrixLayoutSetAttribute(p.c, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &batch, sizeof(batch)));
+    LT_TRY(cublasLtMatrixLayoutSetAttribute(p.a, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &sa, sizeof(sa)));
+    LT_TRY(cublasLtMatrixLayoutSetAttribute(p.b, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &sb, sizeof(sb)));
+    LT_TRY(cublasLtMatrixLayoutSetAttribute(p.c, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &sc, sizeof(sc)));
+    cublasLtMatmulPreference_t pref = nullptr;
+    LT_TRY(cublasLtMatmulPreferenceCreate(&pref));
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &workspace_bytes, sizeof(workspace_bytes));
+    const uint32_t al = (uint32_t)align;
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_A_BYTES, &al, sizeof(al));
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_B_BYTES, &al, sizeof(al));
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_C_BYTES, &al, sizeof(al));
+    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_D_BYTES, &al, sizeof(al));
+    cublasLtMatmulHeuristicResult_t result;
+    int found = 0;
+    const cublasStatus_t s = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, 1, &result, &found);
+    cublasLtMatmulPreferenceDestroy(pref);
+    if (s != CUBLAS_STATUS_SUCCESS || found == 0) {
+      cublasLtMatmulDescDestroy(p.op);
+      cublasLtMatrixLayoutDestroy(p.a);
+      cublasLtMatrixLayoutDestroy(p.b);
+      cublasLtMatrixLayoutDestroy(p.c);
+      return 2;
+    }
+    p.algo = result.algo;
+    it = g_head_plans.emplace(key, p).first;
+  }
+  const Plan& plan = it->second;
+  const float one = 1.0f, zero = 0.0f;
+  LT_TRY(cublasLtMatmul(g_handle, plan.op, &one, w, plan.a, a, plan.b, &zero, out, plan.c, out, plan.c, &plan.algo, workspace,
+                        workspace_bytes, stream));
+  return 0;
+}

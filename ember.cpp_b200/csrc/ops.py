@@ -87,12 +87,15 @@ _SIGNATURES = {
                           _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
     "ember_head_linear": [_c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, ctypes.c_longlong, _c_int, _c_int,
                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_void],
+    "ember_head_linear_bf16": [_c_void, ctypes.c_longlong, _c_int, _c_void, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_int,
+                               _c_int, _c_int, _c_void, _c_size, _c_void],
     "ember_latent_attention_plain": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_int,
                                      _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
     "ember_latent_attention_mma": [_c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void],
     "ember_delta_rule": [_c_void, _c_void, ctypes.c_longlong, _c_int, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void,
-                         _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
+                         _c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                         _c_int, _c_void],
     "ember_sample": [_c_void, _c_void, _c_int, _c_int, _c_float, _c_int, _c_float, _c_u64, _c_void, _c_void, _c_u64, _c_void],
 }
 
@@ -154,7 +157,7 @@ def load_library() -> ctypes.CDLL:
     lib.ember_ssd_scan_scratch.restype = _c_size
     lib.ember_latent_attention_mma_scratch.argtypes = [_c_int] * 3
     lib.ember_latent_attention_mma_scratch.restype = _c_size
-    lib.ember_delta_rule_scratch.argtypes = [_c_int] * 4
+    lib.ember_delta_rule_scratch.argtypes = [_c_int] * 6
     lib.ember_delta_rule_scratch.restype = _c_size
     lib.ember_attention_decode_kept_scratch.argtypes = [_c_int] * 4
     lib.ember_attention_decode_kept_scratch.restype = _c_size
@@ -885,6 +888,14 @@ class CudaOps:
             raise KernelError("head_linear: rows, matrices and output of one element type")
         if a_col + (heads - 1) * a_head + K > a.shape[1] or out_col + (heads - 1) * out_head + N > out.shape[1]:
             raise KernelError("head_linear: the heads do not fit the rows")
+        if w.dtype == torch.bfloat16 and T > SMALL_M and self.gemm == "lt":
+            # the library's strided batch (a head's offset as the batch stride), where everything lies on 16 bytes
+            ws = self._lt_workspace()
+            rc = self._call("ember_head_linear_bf16", a.data_ptr() + 2 * int(a_col), a.stride(0), int(a_head),
+                            self._dense(w, "matrices").data_ptr(), out.data_ptr() + 2 * int(out_col), out.stride(0), int(out_head),
+                            T, heads, N, K, ws.data_ptr(), ws.numel(), allow=(2,))
+            if rc == 0:
+                return out
         self._call("ember_head_linear", a.data_ptr(), a.stride(0), int(a_col), int(a_head), self._dense(w, "matrices").data_ptr(),
                    out.data_ptr(), out.stride(0), int(out_col), int(out_head), T, heads, N, K, _code(w.dtype))
         return out
@@ -924,10 +935,16 @@ class CudaOps:
         return out
 
     # ------------------------------------------------------------------ gated delta rule
-    def delta_rule(self, qkv, proj, b_col, a_col, a_log, dt_bias, state, plan, heads, kv_heads, dim, vdim, unit_eps):
+    DELTA_CHUNKS_FROM = 64   # new tokens of a step's longest sequence from which the delta rule runs in chunks (bfloat16)
+
+    def delta_rule(self, qkv, proj, b_col, a_col, a_log, dt_bias, state, plan, heads, kv_heads, dim, vdim, unit_eps,
+                   chunked=None):
         """The recurrence of parts/delta.py over the step's sequences: qkv [T, q | k | v] (the convolution's output),
         the raw beta and step in `heads` columns each from b_col and a_col of `proj`, state float32
-        [slots, heads, dim, vdim] (advanced); float32 o [T, heads * vdim]."""
+        [slots, heads, dim, vdim] (advanced); float32 o [T, heads * vdim].  chunked: the closed form over chunks of 64
+        tokens (prompts; None lets the step's shape and the element type decide: bfloat16 steps with a sequence of
+        DELTA_CHUNKS_FROM new tokens or more, key sizes that are multiples of 4 up to 128); else token by token, the
+        sums in one fixed order (the 32-bit path, one-token steps)."""
         T = qkv.shape[0]
         if qkv.shape[1] != 2 * kv_heads * dim + heads * vdim or qkv.dtype != proj.dtype:
             raise KernelError("delta_rule: rows of q | k | v in the projection's element type")
@@ -935,12 +952,17 @@ class CudaOps:
             raise KernelError("delta_rule: the state is float32 [slots, heads, dim, vdim]")
         self._dense(qkv, "q | k | v")
         out = torch.empty((T, heads * vdim), dtype=torch.float32, device=qkv.device)
-        scratch = torch.empty(self.lib.ember_delta_rule_scratch(T, heads, kv_heads, dim), dtype=torch.float32, device=qkv.device)
+        if chunked is None:
+            chunked = qkv.dtype == torch.bfloat16 and plan.max_new >= self.DELTA_CHUNKS_FROM
+        chunked = bool(chunked) and dim % 4 == 0 and dim <= 128
+        slots = (T // 64 + plan.n) if chunked else 0        # chunks are numbered through the sequences: at most this many
+        scratch = torch.empty(self.lib.ember_delta_rule_scratch(T, heads, kv_heads, dim, vdim, slots), dtype=torch.float32,
+                              device=qkv.device)
         self._call("ember_delta_rule", qkv.data_ptr(), proj.data_ptr(), proj.stride(0), int(b_col), int(a_col), a_log.data_ptr(),
                    dt_bias.data_ptr(), state.data_ptr(), out.data_ptr(), scratch.data_ptr(), plan.seq_slot.data_ptr(),
                    plan.seq_start.data_ptr(), plan.cu_new.data_ptr(), T, plan.n, heads, kv_heads, dim, vdim, float(unit_eps),
-                   _code(qkv.dtype))
-        self.launches += 1      # (the prepare kernel)
+                   max(int(plan.max_new), 1), slots, _code(qkv.dtype))
+        self.launches += 2 if chunked else 1      # (the prepare kernel, the chunks' factors)
         return out
 
     # ------------------------------------------------------------------ experts by table

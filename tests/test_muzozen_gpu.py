@@ -295,6 +295,40 @@ def test_convolution_delta_rule_and_gated_norm_over_steps(ops, dtype, heads, kv,
         close(torch.cat([g[2] for g in got[s]]), want.reshape(n, inner), OP_TOL[dtype])
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, kv, dim, vdim, alog_mean", [(3, 1, 64, 40, -2.0), (2, 2, 128, 128, -1.0), (4, 2, 16, 8, 2.0), (1, 1, 36, 33, 0.0)])
+def test_the_delta_rule_in_chunks(ops, dtype, heads, kv, dim, vdim, alog_mean):
+    """Prompts run the rule's closed form over chunks of 64 tokens: unequal sequences, continued from carried state,
+    chunk edges inside and at the end of a sequence, weak and strong decay; against the plain recurrence and against
+    the token-by-token kernel on the same rows."""
+    dt = DT[dtype]
+    qk, inner = kv * dim, heads * vdim
+    dtb, alog = rnd(3, heads, scale=0.5) - 1, rnd(4, heads, scale=0.5) + alog_mean
+    lengths = {0: 300, 1: 70, 2: 200, 3: 129}
+    rows = {s: rnd(20 + s, n, 2 * qk + inner).to(dt) for s, n in lengths.items()}
+    ba = {s: rnd(30 + s, n, 8 + 2 * heads, scale=2.0).to(dt) for s, n in lengths.items()}
+    states = {form: torch.full((4, heads, dim, vdim), float("nan")).cuda() for form in (True, False)}
+    got = {form: {s: [] for s in lengths} for form in (True, False)}
+    at = {s: 0 for s in lengths}
+    for step in ([(0, 150), (1, 70), (2, 1), (3, 64)], [(2, 199), (0, 150), (3, 65)]):
+        plan = plan_of([(s, at[s], n) for s, n in step])
+        x = torch.cat([rows[s][at[s]:at[s] + n] for s, n in step]).cuda()
+        p = torch.cat([ba[s][at[s]:at[s] + n] for s, n in step]).cuda()
+        for form in (True, False):
+            o = ops.delta_rule(x, p, 8, 8 + heads, alog.cuda(), dtb.cuda(), states[form], plan, heads, kv, dim, vdim, 1e-6, chunked=form)
+            row = 0
+            for s, n in step:
+                got[form][s].append(o[row:row + n])
+                row += n
+        for s, n in step:
+            at[s] += n
+    for s, n in lengths.items():
+        want = plain_delta_rows(f64(rows[s]), f64(ba[s])[:, 8:], heads, kv, dim, vdim, f64(alog), f64(dtb))
+        close(torch.cat(got[False][s]), want, 5e-5)
+        close(torch.cat(got[True][s]), want, 1e-4)
+    close(states[True], f64(states[False]), 1e-4)
+
+
 def test_the_delta_rule_reads_back_a_value_written_far_back(ops):
     """Almost no decay, orthogonal keys: the value written under a key 600 tokens back is what a query along that
     key reads at the end, and a later write under the same key replaces it."""
