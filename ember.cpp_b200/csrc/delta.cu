@@ -201,6 +201,12 @@ __global__ void delta_scan_wide_kernel(const float* __restrict__ qk, const T* __
 constexpr int kChunk = 64;
 constexpr int kTile = 32;    // value columns a block of the scan
 
+__device__ __forceinline__ void copy16(float* dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(a), "l"(src));
+}
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory"); }
+
 // The chunk slot of sequence s's chunk c: chunks are numbered through the step's sequences in order.
 __device__ __forceinline__ int chunk_slot(const int* cu_new, int s, int c) {
   int base = 0;
@@ -220,11 +226,11 @@ delta_chunk_factor_kernel(const float* __restrict__ qk, const T* __restrict__ qk
   const int t0 = cu_new[s], n = cu_new[s + 1] - t0;
   if (seq_slot[s] < 0 || c * kChunk >= n) return;
   const int rows = min(kChunk, n - c * kChunk), first = t0 + c * kChunk;
-  const int kh = h / (heads / kv_heads), qk_row = 2 * kv_heads * dim, DS = dim + 1, CS = kChunk + 1;
+  const int kh = h / (heads / kv_heads), qk_row = 2 * kv_heads * dim, DS = dim + 1, CS = kChunk + 4;
   float* ks = sm;                       // [64][dim + 1]
   float* qs = ks + kChunk * DS;         // [64][dim + 1]
-  float* am = qs + kChunk * DS;         // [64][65]: A, then Tm scaled for Wk
-  float* tm = am + kChunk * CS;         // [64][65]: Tm
+  float* am = qs + kChunk * DS + (4 - (2 * kChunk * DS) % 4) % 4;   // [64][68]: A, then Tm scaled for Wk (on 16 bytes)
+  float* tm = am + kChunk * CS;         // [64][68]: Tm
   float* lg = tm + kChunk * CS;         // [64] L_t
   float* bt = lg + kChunk;              // [64] beta_t
   float* raw = bt + kChunk;             // [64] log g_t
@@ -250,19 +256,48 @@ delta_chunk_factor_kernel(const float* __restrict__ qk, const T* __restrict__ qk
   __syncthreads();
   const size_t slot = ((size_t)chunk_slot(cu_new, s, c) * heads + h) * kChunk;
   if (tid < kChunk) lgc[slot + tid] = lg[tid];
-  // A and P: thread (i = tid % 64, rows t = tid / 64 + 4 j)
+  // A and P in 4 x 4 tiles of (t, i), a thread a tile of the lower triangle
   {
-    const int i = tid & 63;
-    for (int t = tid >> 6; t < kChunk; t += 4) {
-      float kk = 0.f, qk_dot = 0.f;
+    const int tt = (tid >> 4) * 4, ii = (tid & 15) * 4;
+    if (ii <= tt) {
+      float kk[4][4], qd[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) kk[a][b] = qd[a][b] = 0.f;
       for (int d = 0; d < dim; ++d) {
-        const float ki = ks[i * DS + d];
-        kk = fmaf(ks[t * DS + d], ki, kk);
-        qk_dot = fmaf(qs[t * DS + d], ki, qk_dot);
+        float kt[4], qt[4], ki[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          kt[a] = ks[(tt + a) * DS + d];
+          qt[a] = qs[(tt + a) * DS + d];
+          ki[a] = ks[(ii + a) * DS + d];
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            kk[a][b] = fmaf(kt[a], ki[b], kk[a][b]);
+            qd[a][b] = fmaf(qt[a], ki[b], qd[a][b]);
+          }
       }
-      const float w = i <= t ? expf(lg[t] - lg[i]) : 0.f;
-      am[t * CS + i] = i < t ? bt[t] * w * kk : 0.f;
-      pm[(slot + t) * kChunk + i] = w * qk_dot;
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int t = tt + a, i = ii + b;
+          const float w = i <= t ? expf(lg[t] - lg[i]) : 0.f;
+          am[t * CS + i] = i < t ? bt[t] * w * kk[a][b] : 0.f;
+          pm[(slot + t) * kChunk + i] = w * qd[a][b];
+        }
+    } else {
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          am[(tt + a) * CS + ii + b] = 0.f;
+          pm[(slot + tt + a) * kChunk + ii + b] = 0.f;
+        }
     }
   }
   __syncthreads();
@@ -285,13 +320,20 @@ delta_chunk_factor_kernel(const float* __restrict__ qk, const T* __restrict__ qk
   }
   __syncthreads();
   const int rg = tid >> 5, lane = tid & 31;
+  const int quads = (rows + 3) / 4;         // (rows past the sequence's end have beta = 0: their columns of Tm are zero)
   for (int c0 = 0; c0 < vdim; c0 += 32) {   // Wv: rows rg + 8 j, column c0 + lane
     const int col = c0 + lane;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int i = 0; i < rows; ++i) {
-      const float v = col < vdim ? to_float(qkv[(size_t)(first + i) * channels + 2 * kv_heads * dim + (size_t)h * vdim + col]) : 0.f;
+    const T* vsrc = qkv + (size_t)first * channels + 2 * kv_heads * dim + (size_t)h * vdim + col;
+    for (int iq = 0; iq < quads; ++iq) {
+      float v[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = fmaf(tm[(rg + 8 * j) * CS + i], v, acc[j]);
+      for (int b = 0; b < 4; ++b) v[b] = (col < vdim && 4 * iq + b < rows) ? to_float(vsrc[(size_t)(4 * iq + b) * channels]) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 tv = *reinterpret_cast<const float4*>(tm + (rg + 8 * j) * CS + 4 * iq);
+        acc[j] = fmaf(tv.x, v[0], fmaf(tv.y, v[1], fmaf(tv.z, v[2], fmaf(tv.w, v[3], acc[j]))));
+      }
     }
     if (col < vdim)
 #pragma unroll
@@ -300,10 +342,15 @@ delta_chunk_factor_kernel(const float* __restrict__ qk, const T* __restrict__ qk
   for (int c0 = 0; c0 < dim; c0 += 32) {    // Wk
     const int col = c0 + lane;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int i = 0; i < rows; ++i) {
-      const float v = col < dim ? ks[i * DS + col] : 0.f;
+    for (int iq = 0; iq < quads; ++iq) {
+      float v[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc[j] = fmaf(am[(rg + 8 * j) * CS + i], v, acc[j]);
+      for (int b = 0; b < 4; ++b) v[b] = col < dim ? ks[(4 * iq + b) * DS + col] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 tv = *reinterpret_cast<const float4*>(am + (rg + 8 * j) * CS + 4 * iq);
+        acc[j] = fmaf(tv.x, v[0], fmaf(tv.y, v[1], fmaf(tv.z, v[2], fmaf(tv.w, v[3], acc[j]))));
+      }
     }
     if (col < dim)
 #pragma unroll
@@ -343,21 +390,31 @@ delta_chunk_scan_kernel(const float* __restrict__ qk, const float* __restrict__ 
   for (int d = rg; d < dim; d += 8) ss[d * kTile + lane] = (live && carried) ? st[(size_t)d * vdim + col] : 0.f;
   const int base = chunk_slot(cu_new, s, 0);
   const int n_chunks = (n + kChunk - 1) / kChunk;
+  const int per = (dim + 31) / 32 * 4;      // rows of the state a thread updates: eight runs cover dim (a multiple of 4, up to 128)
   for (int c = 0; c < n_chunks; ++c) {
     const int rows = min(kChunk, n - c * kChunk), first = t0 + c * kChunk;
     const size_t cs = ((size_t)(base + c) * heads + h) * kChunk;
     __syncthreads();   // the chunk before is done with the tiles
+    // the chunk's tiles by 16-byte asynchronous copies, all in flight together
     for (int e = tid * 4; e < kChunk * dim; e += 1024) {
       const int r = e / dim, d = e % dim;
-      *reinterpret_cast<float4*>(wks + e) = *reinterpret_cast<const float4*>(wk + cs * dim + e);
+      copy16(wks + e, wk + cs * dim + e);
       const float* src = qk + (size_t)(first + r) * qk_row;
-      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-      *reinterpret_cast<float4*>(qs + e) = r < rows ? *reinterpret_cast<const float4*>(src + (size_t)kh * dim + d) : zero;
-      *reinterpret_cast<float4*>(ks + e) = r < rows ? *reinterpret_cast<const float4*>(src + (size_t)(kv_heads + kh) * dim + d) : zero;
+      if (r < rows) {
+        copy16(qs + e, src + (size_t)kh * dim + d);
+        copy16(ks + e, src + (size_t)(kv_heads + kh) * dim + d);
+      } else {
+        *reinterpret_cast<float4*>(qs + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(ks + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
     }
-    for (int e = tid * 4; e < kChunk * kChunk; e += 1024)
-      *reinterpret_cast<float4*>(ps + e) = *reinterpret_cast<const float4*>(pm + cs * kChunk + e);
-    for (int r = rg; r < kChunk; r += 8) us[r * kTile + lane] = live ? wv[(cs + r) * vdim + col] : 0.f;
+    for (int e = tid * 4; e < kChunk * kChunk; e += 1024) copy16(ps + e, pm + cs * kChunk + e);
+    if (vdim % 4 == 0 && c0 + kTile <= vdim) {
+      for (int e = tid * 4; e < kChunk * kTile; e += 1024) copy16(us + e, wv + (cs + e / kTile) * vdim + c0 + e % kTile);
+    } else {
+      for (int r = rg; r < kChunk; r += 8) us[r * kTile + lane] = live ? wv[(cs + r) * vdim + col] : 0.f;
+    }
+    copies_wait();
     if (tid < kChunk) lg[tid] = lgc[cs + tid];
     __syncthreads();
     if (tid < kChunk) wj[tid] = tid < rows ? expf(lg[kChunk - 1] - lg[tid]) : 0.f;
@@ -379,20 +436,48 @@ delta_chunk_scan_kernel(const float* __restrict__ qk, const float* __restrict__ 
 #pragma unroll
     for (int j = 0; j < 8; ++j) us[(rg + 8 * j) * kTile + lane] -= au[j];
     __syncthreads();
-    // O = e^L (Q S0) + P U
+    // O = e^L (Q S0) + P U (P is zero above its diagonal)
+    float o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = expf(lg[rg + 8 * j]) * aq[j];
+    for (int i = 0; i < kChunk; i += 4) {
+      const float u0 = us[i * kTile + lane], u1 = us[(i + 1) * kTile + lane], u2 = us[(i + 2) * kTile + lane],
+                  u3 = us[(i + 3) * kTile + lane];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float4 pv = *reinterpret_cast<const float4*>(ps + (rg + 8 * j) * kChunk + i);
+        o[j] = fmaf(pv.x, u0, fmaf(pv.y, u1, fmaf(pv.z, u2, fmaf(pv.w, u3, o[j]))));
+      }
+    }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int r = rg + 8 * j;
-      float o = expf(lg[r]) * aq[j];
-      for (int i = 0; i <= r; ++i) o = fmaf(ps[r * kChunk + i], us[i * kTile + lane], o);
-      if (live && r < rows) out[(size_t)(first + r) * inner + (size_t)h * vdim + col] = o;
+      if (live && r < rows) out[(size_t)(first + r) * inner + (size_t)h * vdim + col] = o[j];
     }
-    // S <- e^(L_end) S0 + sum_i e^(L_end - L_i) k_i u_i^T for the state's rows rg + 8 j
-    const float tail = expf(lg[kChunk - 1]);
-    for (int d = rg; d < dim; d += 8) {
-      float v = tail * ss[d * kTile + lane];
-      for (int i = 0; i < rows; ++i) v = fmaf(wj[i] * ks[i * dim + d], us[i * kTile + lane], v);
-      ss[d * kTile + lane] = v;
+    // S <- e^(L_end) S0 + sum_i e^(L_end - L_i) k_i u_i^T: a thread keeps a run of the state's rows of its column
+    {
+      const float tail = expf(lg[kChunk - 1]);
+      const int d0 = rg * per;
+      float acc[16];
+#pragma unroll
+      for (int j = 0; j < 16; ++j) acc[j] = (j < per && d0 + j < dim) ? tail * ss[(d0 + j) * kTile + lane] : 0.f;
+      for (int i = 0; i < rows; ++i) {
+        const float u = wj[i] * us[i * kTile + lane];
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          if (4 * j4 < per && d0 + 4 * j4 < dim) {
+            const float4 kv = *reinterpret_cast<const float4*>(ks + i * dim + d0 + 4 * j4);
+            acc[4 * j4] = fmaf(kv.x, u, acc[4 * j4]);
+            acc[4 * j4 + 1] = fmaf(kv.y, u, acc[4 * j4 + 1]);
+            acc[4 * j4 + 2] = fmaf(kv.z, u, acc[4 * j4 + 2]);
+            acc[4 * j4 + 3] = fmaf(kv.w, u, acc[4 * j4 + 3]);
+          }
+        }
+      }
+      __syncthreads();   // every thread has read the state's old columns (in U and Q S0 above)
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        if (j < per && d0 + j < dim) ss[(d0 + j) * kTile + lane] = acc[j];
     }
   }
   __syncthreads();
@@ -419,7 +504,7 @@ int delta_rule_run(const T* qkv, const T* proj, long long proj_stride, int b_col
     float* wk = wv + (size_t)chunk_slots * heads * kChunk * vdim;           // [chunk slots][heads][64][dim]
     float* pm = wk + (size_t)chunk_slots * heads * kChunk * dim;            // [chunk slots][heads][64][64]
     float* lgc = pm + (size_t)chunk_slots * heads * kChunk * kChunk;        // [chunk slots][heads][64]: the sums of logarithms
-    const size_t smem1 = (size_t)(2 * kChunk * (dim + 1) + 2 * kChunk * (kChunk + 1) + 3 * kChunk) * sizeof(float);
+    const size_t smem1 = (size_t)(2 * kChunk * (dim + 1) + 4 + 2 * kChunk * (kChunk + 4) + 3 * kChunk) * sizeof(float);
     const size_t smem2 = (size_t)(3 * kChunk * dim + kChunk * kChunk + kChunk * kTile + dim * kTile + 2 * kChunk) * sizeof(float);
     static bool raised[64] = {false};
     int dev = 0;
