@@ -195,11 +195,10 @@ __global__ void delta_scan_wide_kernel(const float* __restrict__ qk, const T* __
 //     Wv = Tm diag(beta) V,   Wk = Tm diag(beta e^L) K,   P[t][i] = e^(L_t - L_i) (q_t . k_i) for i <= t
 // depend on the chunk alone (`delta_chunk_factor`, a block a (chunk, head), all chunks side by side), and then
 //     U = Wv - Wk S0,   O = diag(e^L) Q S0 + P U,   S <- e^(L_end) S0 + sum_i e^(L_end - L_i) k_i u_i^T
-// walk the chunks in order (`delta_chunk_scan`, a block a (sequence, head, 32 value columns): the columns of S are
+// walk the chunks in order (`delta_chunk_scan`, a block a (sequence, head, 32 or 16 value columns): the columns of S are
 // independent).  Every exponent is of a difference <= 0.  All float32 on the CUDA cores; a chunk's rows past the
 // sequence's end count as beta = 0, g = 1 and zero vectors.
 constexpr int kChunk = 64;
-constexpr int kTile = 32;    // value columns a block of the scan
 
 __device__ __forceinline__ void copy16(float* dst, const float* src) {
   const unsigned a = (unsigned)__cvta_generic_to_shared(dst);
@@ -358,115 +357,126 @@ delta_chunk_factor_kernel(const float* __restrict__ qk, const T* __restrict__ qk
   }
 }
 
+// TILE value columns a block (32, or 16 where that is what fills the chip); 256 threads = 256 / TILE groups of rows.
+// Rows of the tiles are padded by four values so that two neighbouring rows, read by the two halves of a warp at
+// TILE = 16, lie in different banks.
+template <int TILE>
 __global__ void __launch_bounds__(256)
 delta_chunk_scan_kernel(const float* __restrict__ qk, const float* __restrict__ wv, const float* __restrict__ wk,
                         const float* __restrict__ pm, const float* __restrict__ lgc, float* __restrict__ state,
                         float* __restrict__ out, const int* __restrict__ seq_slot, const int* __restrict__ seq_start,
                         const int* __restrict__ cu_new, int n_seq, int heads, int kv_heads, int dim, int vdim) {
+  constexpr int NRG = 256 / TILE;          // groups of rows
+  constexpr int RPT = kChunk / NRG;        // rows of a chunk a thread
+  constexpr int PS = kChunk + 4;           // row stride of P
   extern __shared__ __align__(16) float sm[];
-  float* wks = sm;                          // [64][dim]
-  float* qs = wks + kChunk * dim;           // [64][dim]
-  float* ks = qs + kChunk * dim;            // [64][dim]
-  float* ps = ks + kChunk * dim;            // [64][64]
-  float* us = ps + kChunk * kChunk;         // [64][32]: Wv's columns, then U
-  float* ss = us + kChunk * kTile;          // [dim][32]: the state's columns
-  float* lg = ss + dim * kTile;             // [64] L_t
+  const int DP = dim + 4;                   // row stride of the tiles Wk, Q, K
+  float* wks = sm;                          // [64][dim + 4]
+  float* qs = wks + kChunk * DP;            // [64][dim + 4]
+  float* ks = qs + kChunk * DP;             // [64][dim + 4]
+  float* ps = ks + kChunk * DP;             // [64][68]
+  float* us = ps + kChunk * PS;             // [64][TILE]: Wv's columns, then U
+  float* ss = us + kChunk * TILE;           // [dim][TILE]: the state's columns
+  float* lg = ss + dim * TILE;              // [64] L_t
   float* wj = lg + kChunk;                  // [64] e^(L_end - L_t)
-  const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * kTile;
-  const int tid = threadIdx.x, lane = tid & 31, rg = tid >> 5;
-  const int col = c0 + lane;
+  const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * TILE;
+  const int tid = threadIdx.x, cl = tid % TILE, rg = tid / TILE;
+  const int col = c0 + cl;
   const bool live = col < vdim;
   const int t0 = cu_new[s], n = cu_new[s + 1] - t0;
   const int slot = seq_slot[s];
   const int inner = heads * vdim;
   if (slot < 0) {
     if (live)
-      for (int i = rg; i < n; i += 8) out[(size_t)(t0 + i) * inner + (size_t)h * vdim + col] = 0.f;
+      for (int i = rg; i < n; i += NRG) out[(size_t)(t0 + i) * inner + (size_t)h * vdim + col] = 0.f;
     return;
   }
   const int kh = h / (heads / kv_heads), qk_row = 2 * kv_heads * dim;
   float* st = state + ((size_t)slot * heads + h) * dim * vdim;
   const bool carried = seq_start[s] > 0;
-  for (int d = rg; d < dim; d += 8) ss[d * kTile + lane] = (live && carried) ? st[(size_t)d * vdim + col] : 0.f;
+  for (int d = rg; d < dim; d += NRG) ss[d * TILE + cl] = (live && carried) ? st[(size_t)d * vdim + col] : 0.f;
   const int base = chunk_slot(cu_new, s, 0);
   const int n_chunks = (n + kChunk - 1) / kChunk;
-  const int per = (dim + 31) / 32 * 4;      // rows of the state a thread updates: eight runs cover dim (a multiple of 4, up to 128)
+  const int per = (dim + 4 * NRG - 1) / (4 * NRG) * 4;   // rows of the state a thread updates: NRG runs cover dim
+  const int vecs = dim / 4;
   for (int c = 0; c < n_chunks; ++c) {
     const int rows = min(kChunk, n - c * kChunk), first = t0 + c * kChunk;
     const size_t cs = ((size_t)(base + c) * heads + h) * kChunk;
     __syncthreads();   // the chunk before is done with the tiles
     // the chunk's tiles by 16-byte asynchronous copies, all in flight together
-    for (int e = tid * 4; e < kChunk * dim; e += 1024) {
-      const int r = e / dim, d = e % dim;
-      copy16(wks + e, wk + cs * dim + e);
+    for (int e = tid; e < kChunk * vecs; e += 256) {
+      const int r = e / vecs, d = (e % vecs) * 4;
+      copy16(wks + r * DP + d, wk + (cs + r) * dim + d);
       const float* src = qk + (size_t)(first + r) * qk_row;
       if (r < rows) {
-        copy16(qs + e, src + (size_t)kh * dim + d);
-        copy16(ks + e, src + (size_t)(kv_heads + kh) * dim + d);
+        copy16(qs + r * DP + d, src + (size_t)kh * dim + d);
+        copy16(ks + r * DP + d, src + (size_t)(kv_heads + kh) * dim + d);
       } else {
-        *reinterpret_cast<float4*>(qs + e) = make_float4(0.f, 0.f, 0.f, 0.f);
-        *reinterpret_cast<float4*>(ks + e) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(qs + r * DP + d) = make_float4(0.f, 0.f, 0.f, 0.f);
+        *reinterpret_cast<float4*>(ks + r * DP + d) = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    for (int e = tid * 4; e < kChunk * kChunk; e += 1024) copy16(ps + e, pm + cs * kChunk + e);
-    if (vdim % 4 == 0 && c0 + kTile <= vdim) {
-      for (int e = tid * 4; e < kChunk * kTile; e += 1024) copy16(us + e, wv + (cs + e / kTile) * vdim + c0 + e % kTile);
+    for (int e = tid; e < kChunk * (kChunk / 4); e += 256) {
+      const int r = e / (kChunk / 4), i = (e % (kChunk / 4)) * 4;
+      copy16(ps + r * PS + i, pm + (cs + r) * kChunk + i);
+    }
+    if (vdim % 4 == 0 && c0 + TILE <= vdim) {
+      for (int e = tid * 4; e < kChunk * TILE; e += 1024) copy16(us + e, wv + (cs + e / TILE) * vdim + c0 + e % TILE);
     } else {
-      for (int r = rg; r < kChunk; r += 8) us[r * kTile + lane] = live ? wv[(cs + r) * vdim + col] : 0.f;
+      for (int r = rg; r < kChunk; r += NRG) us[r * TILE + cl] = live ? wv[(cs + r) * vdim + col] : 0.f;
     }
     copies_wait();
     if (tid < kChunk) lg[tid] = lgc[cs + tid];
     __syncthreads();
     if (tid < kChunk) wj[tid] = tid < rows ? expf(lg[kChunk - 1] - lg[tid]) : 0.f;
-    // U = Wv - Wk S0 and Q S0 for rows rg + 8 j
-    float au[8], aq[8];
+    // U = Wv - Wk S0 and Q S0 for rows rg + NRG j
+    float au[RPT], aq[RPT];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) au[j] = aq[j] = 0.f;
+    for (int j = 0; j < RPT; ++j) au[j] = aq[j] = 0.f;
     for (int d = 0; d < dim; d += 4) {
-      const float s0 = ss[d * kTile + lane], s1 = ss[(d + 1) * kTile + lane], s2 = ss[(d + 2) * kTile + lane],
-                  s3 = ss[(d + 3) * kTile + lane];
+      const float s0 = ss[d * TILE + cl], s1 = ss[(d + 1) * TILE + cl], s2 = ss[(d + 2) * TILE + cl], s3 = ss[(d + 3) * TILE + cl];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 w = *reinterpret_cast<const float4*>(wks + (rg + 8 * j) * dim + d);
-        const float4 qv = *reinterpret_cast<const float4*>(qs + (rg + 8 * j) * dim + d);
+      for (int j = 0; j < RPT; ++j) {
+        const float4 w = *reinterpret_cast<const float4*>(wks + (rg + NRG * j) * DP + d);
+        const float4 qv = *reinterpret_cast<const float4*>(qs + (rg + NRG * j) * DP + d);
         au[j] = fmaf(w.x, s0, fmaf(w.y, s1, fmaf(w.z, s2, fmaf(w.w, s3, au[j]))));
         aq[j] = fmaf(qv.x, s0, fmaf(qv.y, s1, fmaf(qv.z, s2, fmaf(qv.w, s3, aq[j]))));
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) us[(rg + 8 * j) * kTile + lane] -= au[j];
+    for (int j = 0; j < RPT; ++j) us[(rg + NRG * j) * TILE + cl] -= au[j];
     __syncthreads();
     // O = e^L (Q S0) + P U (P is zero above its diagonal)
-    float o[8];
+    float o[RPT];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) o[j] = expf(lg[rg + 8 * j]) * aq[j];
+    for (int j = 0; j < RPT; ++j) o[j] = expf(lg[rg + NRG * j]) * aq[j];
     for (int i = 0; i < kChunk; i += 4) {
-      const float u0 = us[i * kTile + lane], u1 = us[(i + 1) * kTile + lane], u2 = us[(i + 2) * kTile + lane],
-                  u3 = us[(i + 3) * kTile + lane];
+      const float u0 = us[i * TILE + cl], u1 = us[(i + 1) * TILE + cl], u2 = us[(i + 2) * TILE + cl], u3 = us[(i + 3) * TILE + cl];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float4 pv = *reinterpret_cast<const float4*>(ps + (rg + 8 * j) * kChunk + i);
+      for (int j = 0; j < RPT; ++j) {
+        const float4 pv = *reinterpret_cast<const float4*>(ps + (rg + NRG * j) * PS + i);
         o[j] = fmaf(pv.x, u0, fmaf(pv.y, u1, fmaf(pv.z, u2, fmaf(pv.w, u3, o[j]))));
       }
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int r = rg + 8 * j;
+    for (int j = 0; j < RPT; ++j) {
+      const int r = rg + NRG * j;
       if (live && r < rows) out[(size_t)(first + r) * inner + (size_t)h * vdim + col] = o[j];
     }
     // S <- e^(L_end) S0 + sum_i e^(L_end - L_i) k_i u_i^T: a thread keeps a run of the state's rows of its column
+    // (every thread read the state's old columns before the barrier above; a thread writes only what it owns)
     {
       const float tail = expf(lg[kChunk - 1]);
       const int d0 = rg * per;
       float acc[16];
 #pragma unroll
-      for (int j = 0; j < 16; ++j) acc[j] = (j < per && d0 + j < dim) ? tail * ss[(d0 + j) * kTile + lane] : 0.f;
+      for (int j = 0; j < 16; ++j) acc[j] = (j < per && d0 + j < dim) ? tail * ss[(d0 + j) * TILE + cl] : 0.f;
       for (int i = 0; i < rows; ++i) {
-        const float u = wj[i] * us[i * kTile + lane];
+        const float u = wj[i] * us[i * TILE + cl];
 #pragma unroll
         for (int j4 = 0; j4 < 4; ++j4) {
           if (4 * j4 < per && d0 + 4 * j4 < dim) {
-            const float4 kv = *reinterpret_cast<const float4*>(ks + i * dim + d0 + 4 * j4);
+            const float4 kv = *reinterpret_cast<const float4*>(ks + i * DP + d0 + 4 * j4);
             acc[4 * j4] = fmaf(kv.x, u, acc[4 * j4]);
             acc[4 * j4 + 1] = fmaf(kv.y, u, acc[4 * j4 + 1]);
             acc[4 * j4 + 2] = fmaf(kv.z, u, acc[4 * j4 + 2]);
@@ -474,15 +484,14 @@ delta_chunk_scan_kernel(const float* __restrict__ qk, const float* __restrict__ 
           }
         }
       }
-      __syncthreads();   // every thread has read the state's old columns (in U and Q S0 above)
 #pragma unroll
       for (int j = 0; j < 16; ++j)
-        if (j < per && d0 + j < dim) ss[(d0 + j) * kTile + lane] = acc[j];
+        if (j < per && d0 + j < dim) ss[(d0 + j) * TILE + cl] = acc[j];
     }
   }
   __syncthreads();
   if (live)
-    for (int d = rg; d < dim; d += 8) st[(size_t)d * vdim + col] = ss[d * kTile + lane];
+    for (int d = rg; d < dim; d += NRG) st[(size_t)d * vdim + col] = ss[d * TILE + cl];
 }
 
 template <typename T>
@@ -505,21 +514,28 @@ int delta_rule_run(const T* qkv, const T* proj, long long proj_stride, int b_col
     float* pm = wk + (size_t)chunk_slots * heads * kChunk * dim;            // [chunk slots][heads][64][64]
     float* lgc = pm + (size_t)chunk_slots * heads * kChunk * kChunk;        // [chunk slots][heads][64]: the sums of logarithms
     const size_t smem1 = (size_t)(2 * kChunk * (dim + 1) + 4 + 2 * kChunk * (kChunk + 4) + 3 * kChunk) * sizeof(float);
-    const size_t smem2 = (size_t)(3 * kChunk * dim + kChunk * kChunk + kChunk * kTile + dim * kTile + 2 * kChunk) * sizeof(float);
+    // 16 value columns a block where blocks of 32 would leave SMs without one
+    const int tile = (long long)n_seq * heads * ((vdim + 31) / 32) < sm_count() ? 16 : 32;
+    const size_t smem2 = (size_t)(3 * kChunk * (dim + 4) + kChunk * (kChunk + 4) + kChunk * tile + dim * tile + 2 * kChunk) * sizeof(float);
     static bool raised[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (!raised[dev & 63]) {
       if (cudaFuncSetAttribute(delta_chunk_factor_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024) != cudaSuccess ||
-          cudaFuncSetAttribute(delta_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
+          cudaFuncSetAttribute(delta_chunk_scan_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+          cudaFuncSetAttribute(delta_chunk_scan_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess)
         return ember_fail("delta_rule: the chunk kernels' shared memory could not be raised");
       raised[dev & 63] = true;
     }
     delta_chunk_factor_kernel<T><<<dim3(n_seq * max_chunks, heads), 256, smem1, stream>>>(
         qk, qkv, beta, log_decay, wv, wk, pm, lgc, seq_slot, cu_new, n_seq, max_chunks, heads, kv_heads, dim, vdim, channels);
     EMBER_LAUNCH_OK("delta_chunk_factor");
-    delta_chunk_scan_kernel<<<dim3(n_seq, heads, (vdim + kTile - 1) / kTile), 256, smem2, stream>>>(
-        qk, wv, wk, pm, lgc, state, out, seq_slot, seq_start, cu_new, n_seq, heads, kv_heads, dim, vdim);
+    if (tile == 16)
+      delta_chunk_scan_kernel<16><<<dim3(n_seq, heads, (vdim + 15) / 16), 256, smem2, stream>>>(
+          qk, wv, wk, pm, lgc, state, out, seq_slot, seq_start, cu_new, n_seq, heads, kv_heads, dim, vdim);
+    else
+      delta_chunk_scan_kernel<32><<<dim3(n_seq, heads, (vdim + 31) / 32), 256, smem2, stream>>>(
+          qk, wv, wk, pm, lgc, state, out, seq_slot, seq_start, cu_new, n_seq, heads, kv_heads, dim, vdim);
     EMBER_LAUNCH_OK("delta_chunk_scan");
     return 0;
   }

@@ -174,14 +174,14 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
   T* o = out + t * n + c0;
   float ss = 0.f;
   if constexpr (VEC) {
-    for (int i = threadIdx.x * 4; i < part; i += kThreads * 4) {
+    for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
       const float4 a = load4(yr + i), g = load4(zr + i);
       const float v0 = GATE_FIRST ? a.x * (g.x * sigmoidf(g.x)) : a.x, v1 = GATE_FIRST ? a.y * (g.y * sigmoidf(g.y)) : a.y,
                   v2 = GATE_FIRST ? a.z * (g.z * sigmoidf(g.z)) : a.z, v3 = GATE_FIRST ? a.w * (g.w * sigmoidf(g.w)) : a.w;
       ss = fmaf(v0, v0, fmaf(v1, v1, fmaf(v2, v2, fmaf(v3, v3, ss))));
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
-    for (int i = threadIdx.x * 4; i < part; i += kThreads * 4) {
+    for (int i = threadIdx.x * 4; i < part; i += blockDim.x * 4) {
       const float4 a = load4(yr + i), g = load4(zr + i), gain = load4(w + c0 + i);
       if constexpr (GATE_FIRST)
         store4(o + i, a.x * (g.x * sigmoidf(g.x)) * inv * gain.x, a.y * (g.y * sigmoidf(g.y)) * inv * gain.y,
@@ -191,13 +191,13 @@ gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ z, lo
                a.z * inv * gain.z * (g.z * sigmoidf(g.z)), a.w * inv * gain.w * (g.w * sigmoidf(g.w)));
     }
   } else {
-    for (int i = threadIdx.x; i < part; i += kThreads) {
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
       const float zv = to_float(zr[i]);
       const float v = GATE_FIRST ? yr[i] * (zv * sigmoidf(zv)) : yr[i];
       ss = fmaf(v, v, ss);
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) / (float)part + eps);
-    for (int i = threadIdx.x; i < part; i += kThreads) {
+    for (int i = threadIdx.x; i < part; i += blockDim.x) {
       const float zv = to_float(zr[i]);
       o[i] = from_float<T>(GATE_FIRST ? yr[i] * (zv * sigmoidf(zv)) * inv * w[c0 + i] : yr[i] * inv * w[c0 + i] * (zv * sigmoidf(zv)));
     }
@@ -272,11 +272,14 @@ EMBER_API int ember_gated_group_norm(const float* y, const void* z, long long z_
   EMBER_CHECK(parts <= 65535, "gated_group_norm: %d parts exceed one launch", parts);
   const dim3 grid(rows, parts);
   const int elem = dtype == EMBER_F32 ? 4 : 2;
+  // a part as short as a head takes a warp or two, not a block of eight that mostly idle
+  const int per_pass = (n / parts + 3) / 4;
+  const int threads = per_pass >= kThreads ? kThreads : (per_pass + 31) / 32 * 32;
   const bool vec = (n / parts) % 4 == 0 && n % 4 == 0 && z_stride % 4 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)w % 16 == 0 &&
                    (uintptr_t)z % (4 * elem) == 0 && (uintptr_t)out % (4 * elem) == 0;
   cudaError_t e;
 #define EMBER_GGN1(T, VEC, FIRST)                                                                                  \
-  launch_plain(gated_group_norm_kernel<T, VEC, FIRST>, grid, dim3(kThreads), 0, stream, y, (const T*)z, z_stride, w, (T*)out, \
+  launch_plain(gated_group_norm_kernel<T, VEC, FIRST>, grid, dim3(threads), 0, stream, y, (const T*)z, z_stride, w, (T*)out, \
                n, n / parts, eps)
 #define EMBER_GGN(T, VEC) (gate_first ? EMBER_GGN1(T, VEC, true) : EMBER_GGN1(T, VEC, false))
   if (dtype == EMBER_F32)
