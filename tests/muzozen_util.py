@@ -62,7 +62,21 @@ CONFIGS = {
         _latent(2, 10, 6, 14, 6, 20, 0.3, ROT_C, kv_from=0),
     ]},
 }
-SEEDS = {"muz_a": 11, "muz_b": 12, "muz_c": 13}
+# odd sizes everywhere, only delta-rule layers in front of one attention layer that nothing shares, a key part of two values
+CONFIGS["muz_d"] = {"architecture": "Muzozen", "vocab": 77, "width": 36, "norm": {"eps": 1e-6},
+                    "embedding": {"scale": 3.0, "bigram": {"buckets": 13, "mul_prev": 100003, "mul_cur": 99991}}, "layers": [
+    _delta(5, 5, 7, 3, 5, ff=27),
+    _delta(2, 1, 130, 9, 2),
+    _latent(5, 3, 2, 7, 5, 9, 0.4, _rot(2, 37.0, {"factor": 1.5, "original": 16, "fast": 4.0, "slow": 1.0}), ff=11),
+]}
+# only attention layers (no state besides the pair table's), every later one reading the first one's rows
+CONFIGS["muz_e"] = {"architecture": "Muzozen", "vocab": 64, "width": 32, "norm": {"eps": 1e-5},
+                    "embedding": {"scale": 1.0, "bigram": {"buckets": 5, "mul_prev": 1, "mul_cur": 1}}, "layers": [
+    _latent(2, 16, 16, 16, 16, 32, 0.2, ROT_A, ff=48),
+    _latent(4, 8, 16, 8, 8, 32, 0.2, ROT_A, kv_from=0),
+    _latent(1, 32, 16, 32, 24, 32, 0.1, ROT_A, kv_from=0, ff=16),
+]}
+SEEDS = {"muz_a": 11, "muz_b": 12, "muz_c": 13, "muz_d": 14, "muz_e": 15}
 
 
 def config(name: str) -> dict:

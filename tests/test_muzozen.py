@@ -123,7 +123,7 @@ def test_plain_state_matters(plains):
 
 
 # ------------------------------------------------------------------------------ the step function over the CPU double
-@pytest.mark.parametrize("name", ["muz_a", "muz_b", "muz_c"])
+@pytest.mark.parametrize("name", ["muz_a", "muz_b", "muz_c", "muz_d", "muz_e"])
 def test_steps_equal_whole_sequences(folders, plains, name):
     """Whole prompts, one token at a time from the first token on, portions down to two tokens, and unequal
     batches decoded together: all give the plain implementation's logits at every position."""

@@ -356,7 +356,7 @@ def engines(folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["muz_a", "muz_b", "muz_c"])
+@pytest.mark.parametrize("name", ["muz_a", "muz_b", "muz_c", "muz_d", "muz_e"])
 def test_prompts_decoding_portions_and_batches_equal_the_plain_model(engines, plains, name, dtype):
     eng, m = engines[(name, dtype)], plains[name]
     vocab = m.cfg["vocab"]
