@@ -4,11 +4,11 @@
 // sequence's new tokens times its heads, token-major, 16 to 64 of them a block.  A block walks the
 // pages of 64 positions that its rows can see; a page's rows c | k_r (rank + rot values a key) come into
 // shared memory once for all the block's rows, the block's query rows stay there from the start.
-// Two warps share a group of 16 rows: each makes the group's scores S = Q K^T for the page (the same
-// work twice, which saves an exchange), keeps its own running maximum and sum, turns S into
-// probabilities in registers, and adds P C to its own half of the output's `rank` columns, which stays
-// in registers (up to 128 float32 values a thread).  Keys past a row's own position are masked by
-// selection; float32 softmax in base 2.
+// Two warps share a group of 16 rows: each makes the group's scores S = Q K^T for half of the page's
+// keys; they tell each other their rows' maxima and hand each other their probabilities (bfloat16)
+// through shared memory, meeting at a barrier of their own, and each adds P C for all 64 keys to its own
+// half of the output's `rank` columns, which stays in registers (up to 128 float32 values a thread).
+// Keys past a row's own position are masked by selection; float32 softmax in base 2.
 //
 // One token a sequence (a decode step): the pages are cut into chunks, a block a chunk (grid z); blocks
 // leave unnormalised sums with their maximum and total, and `latent_merge` combines them.  Otherwise
@@ -47,6 +47,10 @@ __device__ __forceinline__ unsigned pack2(float a, float b) {
 }
 
 constexpr int kKeys = 64;   // keys a tile: one page
+constexpr int kPS = kKeys + 8;   // row stride of the probabilities in shared memory (rows 16 bytes apart in banks)
+
+// The two warps of a group of rows meet (barrier 1 + group; barrier 0 is the block's).
+__device__ __forceinline__ void pair_sync(int g) { asm volatile("bar.sync %0, 64;\n" ::"r"(1 + g) : "memory"); }
 
 // grid (row tiles, sequences, chunks); blockDim.x = 64 * G for G groups of 16 rows.
 template <int RMAX>
@@ -60,6 +64,8 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const
   const int G = blockDim.x >> 6;
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);   // [16 G][WS]
   bf16* ks = qs + (size_t)16 * G * WS;            // [64][WS]
+  bf16* pb = ks + (size_t)kKeys * WS;             // [G][16][kPS]: a group's probabilities of the page
+  float* xb = reinterpret_cast<float*>(pb + (size_t)G * 16 * kPS);   // [G][2][16]: what the two warps of a group tell each other
   const int s = blockIdx.y, chunk = blockIdx.z;
   const int t0 = cu_new[s], n_new = cu_new[s + 1] - t0;
   const int R = n_new * heads, r0 = blockIdx.x * 16 * G;
@@ -113,16 +119,16 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const
     cp_async_wait_all();
     __syncthreads();
 
-    float sa[8][4];
+    float sa[4][4];   // this warp's half of the page's keys: 32 keys from 32 * half
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.f;
+    for (int i = 0; i < 4; ++i) sa[i][0] = sa[i][1] = sa[i][2] = sa[i][3] = 0.f;
     for (int k0 = 0; k0 < W; k0 += 16) {
       unsigned a[4];
       ldsm_x4(a[0], a[1], a[2], a[3], qs + (size_t)(g * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * WS + k0 + 8 * (lane >> 4));
 #pragma unroll
-      for (int np = 0; np < 4; ++np) {
+      for (int np = 0; np < 2; ++np) {
         unsigned b0, b1, b2, b3;
-        ldsm_x4(b0, b1, b2, b3, ks + (size_t)(np * 16 + (lane & 7) + 8 * (lane >> 4)) * WS + k0 + 8 * ((lane >> 3) & 1));
+        ldsm_x4(b0, b1, b2, b3, ks + (size_t)(half * 32 + np * 16 + (lane & 7) + 8 * (lane >> 4)) * WS + k0 + 8 * ((lane >> 3) & 1));
         mma_bf16(sa[2 * np], a, b0, b1);
         mma_bf16(sa[2 * np + 1], a, b2, b3);
       }
@@ -130,10 +136,10 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const
     // scores in base 2, keys past a row's own position masked by selection
     float mx_a = -INFINITY, mx_b = -INFINITY;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
+    for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int j = pg * kPage + nt * 8 + 2 * (lane & 3) + (e & 1);
+        const int j = pg * kPage + half * 32 + nt * 8 + 2 * (lane & 3) + (e & 1);
         const bool top = e < 2;
         const bool seen = page >= 0 && (top ? (ra < R && j <= pa_row) : (rb < R && j <= pb_row));
         const float v = seen ? sa[nt][e] * scale_log2 : -INFINITY;
@@ -145,30 +151,37 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const
     mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
     mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
-    const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+    float* mine = xb + (size_t)(g * 2 + half) * 16;
+    const float* theirs = xb + (size_t)(g * 2 + (half ^ 1)) * 16;
+    if ((lane & 3) == 0) {
+      mine[lane >> 2] = mx_a;
+      mine[(lane >> 2) + 8] = mx_b;
+    }
+    pair_sync(g);
+    const float mn_a = fmaxf(m_a, fmaxf(mx_a, theirs[lane >> 2])), mn_b = fmaxf(m_b, fmaxf(mx_b, theirs[(lane >> 2) + 8]));
     const float corr_a = mn_a == -INFINITY ? 1.f : exp2f(m_a - mn_a), corr_b = mn_b == -INFINITY ? 1.f : exp2f(m_b - mn_b);
     float sum_a = 0.f, sum_b = 0.f;
+    bf16* prow_a = pb + (size_t)(g * 16 + (lane >> 2)) * kPS + half * 32 + 2 * (lane & 3);
+    bf16* prow_b = prow_a + 8 * kPS;
 #pragma unroll
-    for (int nt = 0; nt < 8; ++nt) {
-      sa[nt][0] = mn_a == -INFINITY ? 0.f : exp2f(sa[nt][0] - mn_a);
-      sa[nt][1] = mn_a == -INFINITY ? 0.f : exp2f(sa[nt][1] - mn_a);
-      sa[nt][2] = mn_b == -INFINITY ? 0.f : exp2f(sa[nt][2] - mn_b);
-      sa[nt][3] = mn_b == -INFINITY ? 0.f : exp2f(sa[nt][3] - mn_b);
-      sum_a += sa[nt][0] + sa[nt][1];
-      sum_b += sa[nt][2] + sa[nt][3];
+    for (int nt = 0; nt < 4; ++nt) {
+      const float p0 = mn_a == -INFINITY ? 0.f : exp2f(sa[nt][0] - mn_a), p1 = mn_a == -INFINITY ? 0.f : exp2f(sa[nt][1] - mn_a);
+      const float p2 = mn_b == -INFINITY ? 0.f : exp2f(sa[nt][2] - mn_b), p3 = mn_b == -INFINITY ? 0.f : exp2f(sa[nt][3] - mn_b);
+      sum_a += p0 + p1;
+      sum_b += p2 + p3;
+      *reinterpret_cast<unsigned*>(prow_a + nt * 8) = pack2(p0, p1);
+      *reinterpret_cast<unsigned*>(prow_b + nt * 8) = pack2(p2, p3);
     }
-    l_a = l_a * corr_a + sum_a;
+    l_a = l_a * corr_a + sum_a;   // (this warp's keys; the two warps' totals are added at the end)
     l_b = l_b * corr_b + sum_b;
     m_a = mn_a;
     m_b = mn_b;
+    pair_sync(g);                 // the group's probabilities of all 64 keys are in place
     unsigned pf[4][4];   // the probabilities as the left operand of P C, 16 keys a step
 #pragma unroll
-    for (int kk = 0; kk < 4; ++kk) {
-      pf[kk][0] = pack2(sa[2 * kk][0], sa[2 * kk][1]);
-      pf[kk][1] = pack2(sa[2 * kk][2], sa[2 * kk][3]);
-      pf[kk][2] = pack2(sa[2 * kk + 1][0], sa[2 * kk + 1][1]);
-      pf[kk][3] = pack2(sa[2 * kk + 1][2], sa[2 * kk + 1][3]);
-    }
+    for (int kk = 0; kk < 4; ++kk)
+      ldsm_x4(pf[kk][0], pf[kk][1], pf[kk][2], pf[kk][3],
+              pb + (size_t)(g * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kPS + kk * 16 + 8 * (lane >> 4));
 #pragma unroll
     for (int i = 0; i < RMAX / 32; ++i) {
       if (i < np_count) {
@@ -190,6 +203,17 @@ latent_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kc, const
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
   l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+  {   // the row's total is the two warps' together (both have scaled theirs by the same corrections)
+    float* mine = xb + (size_t)(g * 2 + half) * 16;
+    const float* theirs = xb + (size_t)(g * 2 + (half ^ 1)) * 16;
+    if ((lane & 3) == 0) {
+      mine[lane >> 2] = l_a;
+      mine[(lane >> 2) + 8] = l_b;
+    }
+    pair_sync(g);
+    l_a += theirs[lane >> 2];
+    l_b += theirs[(lane >> 2) + 8];
+  }
   if (n_chunks == 1) {
     const float inv_a = l_a > 0.f ? 1.0f / l_a : 0.f, inv_b = l_b > 0.f ? 1.0f / l_b : 0.f;
 #pragma unroll
@@ -271,7 +295,8 @@ EMBER_API int ember_latent_attention_mma(const void* q, const void* kc, const vo
   const int G = rows >= 64 ? 4 : (int)((rows + 15) / 16);
   const dim3 grid((unsigned)((rows + 16 * G - 1) / (16 * G)), n_seq, n_chunks);
   EMBER_CHECK(n_seq <= 65535 && n_chunks <= 65535, "latent_attention_mma: %d sequences in %d chunks exceed one launch", n_seq, n_chunks);
-  const size_t smem = (size_t)(16 * G + kKeys) * (rank + rot + 8) * sizeof(bf16);
+  const size_t smem = (size_t)(16 * G + kKeys) * (rank + rot + 8) * sizeof(bf16) + (size_t)G * 16 * kPS * sizeof(bf16) +
+                      (size_t)G * 2 * 16 * sizeof(float);
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)T * heads * n_chunks * rank : nullptr;
   EMBER_CHECK(n_chunks == 1 || scratch != nullptr, "latent_attention_mma: chunks need scratch");
