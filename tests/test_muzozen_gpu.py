@@ -165,7 +165,8 @@ def latent_steps(ops, dtype, heads, q_rank, rank, rot, rot_part, steps, down_of,
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("heads, q_rank, rank, rot, dims", [(4, 24, 32, 16, 16), (16, 40, 128, 32, 32), (3, 14, 20, 6, 6), (1, 8, 64, 16, 8),
-                                                            (6, 48, 256, 64, 64), (2, 16, 48, 48, 48), (20, 16, 32, 16, 16)])
+                                                            (6, 48, 256, 64, 64), (2, 16, 48, 48, 48), (20, 16, 32, 16, 16),
+                                                            (2, 16, 512, 64, 64), (3, 16, 96, 16, 16), (2, 8, 320, 32, 32)])
 def test_rows_are_normed_cached_and_attended(ops, dtype, heads, q_rank, rank, rot, dims):
     """Prompts of unequal length, portions on top of a cache, one token each: the query row's norm, the cached row's
     norm, the key part's rotation, and the attention over what the cache holds."""
@@ -327,6 +328,32 @@ def test_the_delta_rule_in_chunks(ops, dtype, heads, kv, dim, vdim, alog_mean):
         close(torch.cat(got[False][s]), want, 5e-5)
         close(torch.cat(got[True][s]), want, 1e-4)
     close(states[True], f64(states[False]), 1e-4)
+
+
+def test_the_delta_rule_in_chunks_with_many_sequences(ops):
+    """Eight sequences of a step are more blocks than the chip has SMs, so a block of the chunk scan takes 32 value
+    columns instead of 16; with carried state from a first step."""
+    heads, kv, dim, vdim = 6, 3, 32, 128
+    qk, inner = kv * dim, heads * vdim
+    dtb, alog = rnd(3, heads, scale=0.5) - 1, rnd(4, heads, scale=0.5) - 1.0
+    lengths = [64, 150, 65, 127, 128, 90, 200, 70]
+    rows = [rnd(20 + s, 2 * n, 2 * qk + inner).bfloat16() for s, n in enumerate(lengths)]
+    ba = [rnd(40 + s, 2 * n, 2 * heads, scale=2.0).bfloat16() for s, n in enumerate(lengths)]
+    states = {form: torch.full((8, heads, dim, vdim), float("nan")).cuda() for form in (True, False)}
+    outs = {True: [], False: []}
+    for part in (0, 1):
+        plan = plan_of([(s, part * n, n) for s, n in enumerate(lengths)])
+        x = torch.cat([rows[s][part * n:(part + 1) * n] for s, n in enumerate(lengths)]).cuda()
+        p = torch.cat([ba[s][part * n:(part + 1) * n] for s, n in enumerate(lengths)]).cuda()
+        for form in (True, False):
+            outs[form].append(ops.delta_rule(x, p, 0, heads, alog.cuda(), dtb.cuda(), states[form], plan, heads, kv, dim, vdim, 1e-6, chunked=form))
+    for a, b in zip(outs[True], outs[False]):
+        close(a, f64(b), 1e-4)
+    close(states[True], f64(states[False]), 1e-4)
+    want = plain_delta_rows(f64(rows[1]), f64(ba[1]), heads, kv, dim, vdim, f64(alog), f64(dtb))
+    at = sum(lengths[:1])
+    got = torch.cat([outs[True][0][at:at + lengths[1]], outs[True][1][at:at + lengths[1]]])
+    close(got, want, 1e-4)
 
 
 def test_the_delta_rule_reads_back_a_value_written_far_back(ops):
